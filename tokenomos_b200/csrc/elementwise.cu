@@ -525,6 +525,35 @@ TK_API int tk_scale_rows(void* x, int64_t total, float scale, int dtype, cudaStr
     return 0;
 }
 
+// out[r, c] = float(x[r, c]) * scale, a new 32-bit tensor: rows of a 16-bit table that start a
+// 32-bit residual stream keep every bit of the product
+template <typename T>
+__global__ void scale_rows_f32_kernel(const T* x, int64_t ld, float* out, float scale, int rows, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = (int64_t)rows * width;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (; i < total; i += step) out[i] = to_f<T>(x[(i / width) * ld + i % width]) * scale;
+}
+
+TK_API int tk_scale_rows_f32(const void* x, int64_t ld, float* out, float scale, int rows, int width, int dtype,
+                             cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && width > 0, "scale_rows_f32: bad sizes");
+    if (rows == 0) return 0;
+    const int64_t want = ((int64_t)rows * width + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == TK_F32)
+        tk_launch(scale_rows_f32_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, ld, out, scale, rows, width);
+    else if (dtype == TK_BF16)
+        tk_launch(scale_rows_f32_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, ld, out,
+                  scale, rows, width);
+    else
+        TK_CHECK_ARG(false, "scale_rows_f32: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("scale_rows_f32");
+    return 0;
+}
+
 // logits [rows, vocab] float32, in place: cap > 0: x = cap * tanh(x / cap); then the `n_suppress`
 // ids of `suppress` (each inside the vocabulary) become -inf in every row
 __global__ void logit_options_kernel(float* logits, int64_t ld, int rows, int vocab, float cap,

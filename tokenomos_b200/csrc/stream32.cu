@@ -17,7 +17,7 @@ template <typename T, int ITEMS>
 __global__ void __launch_bounds__(256)
 stream32_add_norm_kernel(const float* stream_in, const T* x, int64_t x_stride, const T* rows_add,
                          const float* __restrict__ vec_add, const float* __restrict__ w, float eps,
-                         float* stream_out, T* y, int width) {
+                         float* stream_out, T* y, float* y32, int width) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[33];
@@ -44,7 +44,11 @@ stream32_add_norm_kernel(const float* stream_in, const T* x, int64_t x_stride, c
 #pragma unroll
         for (int k = 0; k < ITEMS; ++k) {
             const int i = threadIdx.x + k * blockDim.x;
-            if (i < width) y[r * width + i] = from_f<T>(keep[k] * rstd * w[i]);
+            if (i < width) {
+                const float o = keep[k] * rstd * w[i];
+                if (y != nullptr) y[r * width + i] = from_f<T>(o);
+                if (y32 != nullptr) y32[r * width + i] = o;
+            }
         }
     } else {
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -53,8 +57,11 @@ stream32_add_norm_kernel(const float* stream_in, const T* x, int64_t x_stride, c
         }
         if (w == nullptr) return;
         const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
-        for (int i = threadIdx.x; i < width; i += blockDim.x)
-            y[r * width + i] = from_f<T>(stream_out[r * width + i] * rstd * w[i]);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float o = stream_out[r * width + i] * rstd * w[i];
+            if (y != nullptr) y[r * width + i] = from_f<T>(o);
+            if (y32 != nullptr) y32[r * width + i] = o;
+        }
     }
 }
 
@@ -92,7 +99,7 @@ template <typename T, int ITEMS>
 __global__ void __launch_bounds__(256)
 stream32_add_norm_vec_kernel(const float* stream_in, const T* x, int64_t x_stride, const T* rows_add,
                              const float* __restrict__ vec_add, const float* __restrict__ w, float eps,
-                             float* stream_out, T* y, int width) {
+                             float* stream_out, T* y, float* y32, int width) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[33];
@@ -136,8 +143,10 @@ stream32_add_norm_vec_kernel(const float* stream_in, const T* x, int64_t x_strid
         const int i = (threadIdx.x + k * blockDim.x) * 4;
         if (i < width) {
             const float4 g = *reinterpret_cast<const float4*>(w + i);
-            Quad<T>::store(y + r * width + i, make_float4(keep[k].x * rstd * g.x, keep[k].y * rstd * g.y,
-                                                           keep[k].z * rstd * g.z, keep[k].w * rstd * g.w));
+            const float4 o = make_float4(keep[k].x * rstd * g.x, keep[k].y * rstd * g.y, keep[k].z * rstd * g.z,
+                                         keep[k].w * rstd * g.w);
+            if (y != nullptr) Quad<T>::store(y + r * width + i, o);
+            if (y32 != nullptr) *reinterpret_cast<float4*>(y32 + r * width + i) = o;
         }
     }
 }
@@ -145,29 +154,29 @@ stream32_add_norm_vec_kernel(const float* stream_in, const T* x, int64_t x_strid
 template <typename T>
 static int launch_stream32(const float* stream_in, const void* x, int64_t x_stride, const void* rows_add,
                            const float* vec_add, const float* w, float eps, float* stream_out, void* y,
-                           int rows, int width, cudaStream_t stream) {
+                           float* y32, int rows, int width, cudaStream_t stream) {
     const int threads = width >= 1024 ? 256 : 128;
     const int per_thread = (width + threads - 1) / threads;
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     const bool vec = width % 4 == 0 && x_stride % 4 == 0 && aligned(stream_in) && aligned(stream_out) &&
-                     aligned(vec_add) && aligned(w) && ((uintptr_t)x & 7) == 0 && ((uintptr_t)rows_add & 7) == 0 &&
+                     aligned(vec_add) && aligned(w) && aligned(y32) && ((uintptr_t)x & 7) == 0 && ((uintptr_t)rows_add & 7) == 0 &&
                      ((uintptr_t)y & 7) == 0 && (sizeof(T) == 2 || (aligned(x) && aligned(rows_add) && aligned(y)));
     if (vec && width <= 4 * 2 * threads) {
         tk_launch(stream32_add_norm_vec_kernel<T, 2>, dim3(rows), dim3(threads), 0, stream, stream_in, (const T*)x,
-                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, width);
+                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, y32, width);
         return 0;
     }
     if (vec && width <= 4 * 6 * threads) {
         tk_launch(stream32_add_norm_vec_kernel<T, 6>, dim3(rows), dim3(threads), 0, stream, stream_in, (const T*)x,
-                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, width);
+                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, y32, width);
         return 0;
     }
     if (per_thread <= 8)
         tk_launch(stream32_add_norm_kernel<T, 8>, dim3(rows), dim3(threads), 0, stream, stream_in, (const T*)x,
-                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, width);
+                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, y32, width);
     else
         tk_launch(stream32_add_norm_kernel<T, 0>, dim3(rows), dim3(threads), 0, stream, stream_in, (const T*)x,
-                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, width);
+                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, y32, width);
     return 0;
 }
 
@@ -176,17 +185,17 @@ static int launch_stream32(const float* stream_in, const void* x, int64_t x_stri
 // x: T rows `x_stride` elements apart; rows_add: T [rows, width]; vec_add, w: float [width].
 TK_API int tk_stream32_add_norm(const float* stream_in, const void* x, int64_t x_stride, const void* rows_add,
                                 const float* vec_add, const float* w, float eps, float* stream_out, void* y,
-                                int rows, int width, int dtype, cudaStream_t stream) {
+                                float* y32, int rows, int width, int dtype, cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && width > 0, "stream32_add_norm: bad sizes rows=%d width=%d", rows, width);
     TK_CHECK_ARG(stream_in != nullptr || x != nullptr || rows_add != nullptr, "stream32_add_norm: nothing to add up");
     TK_CHECK_ARG(stream_out != nullptr || (w != nullptr && width <= 2048),
                  "stream32_add_norm: a row of %d without a stream to write", width);
-    TK_CHECK_ARG(w == nullptr || y != nullptr, "stream32_add_norm: a norm weight without an output");
+    TK_CHECK_ARG(w == nullptr || y != nullptr || y32 != nullptr, "stream32_add_norm: a norm weight without an output");
     if (rows == 0) return 0;
     if (dtype == TK_F32)
-        launch_stream32<float>(stream_in, x, x_stride, rows_add, vec_add, w, eps, stream_out, y, rows, width, stream);
+        launch_stream32<float>(stream_in, x, x_stride, rows_add, vec_add, w, eps, stream_out, y, y32, rows, width, stream);
     else if (dtype == TK_BF16)
-        launch_stream32<__nv_bfloat16>(stream_in, x, x_stride, rows_add, vec_add, w, eps, stream_out, y, rows,
+        launch_stream32<__nv_bfloat16>(stream_in, x, x_stride, rows_add, vec_add, w, eps, stream_out, y, y32, rows,
                                        width, stream);
     else
         TK_CHECK_ARG(false, "stream32_add_norm: unknown dtype %d", dtype);

@@ -17,6 +17,7 @@ import torch
 from tokenomos_b200.models.darizen import Darizen
 from tokenomos_b200.models.laposun import Laposun
 from tokenomos_b200.models.lfm3 import Lfm3
+from tokenomos_b200.models.lisorax import Lisorax
 from tokenomos_b200.parts import build_model
 from tokenomos_b200.parts.registry import Runtime, Tuning
 from tokenomos_b200.weights.checkpoint import Checkpoint, load_tensors
@@ -95,3 +96,4 @@ def from_tensors(conf: Configured, tensors: dict, device: torch.device | str = "
 register(Lfm3())
 register(Darizen())
 register(Laposun())
+register(Lisorax())

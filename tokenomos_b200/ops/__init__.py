@@ -315,12 +315,13 @@ def rotary_write(qkv: torch.Tensor, kv_pool: torch.Tensor | None, freq: torch.Te
 
 def stream32_add_norm(stream: torch.Tensor | None, x: torch.Tensor | None, weight: torch.Tensor | None,
                       eps: float, rows_add: torch.Tensor | None = None, vec_add: torch.Tensor | None = None,
-                      out_dtype: torch.dtype | None = None, in_place: bool = False):
+                      out_dtype: torch.dtype | None = None, in_place: bool = False, wide: bool = False):
     """A residual stream kept in 32-bit: ``stream' = stream + x + rows_add + vec_add`` (each
     optional, ``stream`` float32 [rows, width], ``x`` and ``rows_add`` in the model's storage type,
     ``vec_add`` float32 [width]) and ``y = rmsnorm(stream') * weight`` in ``out_dtype`` (default: the
     type of ``x`` / ``rows_add``), rounded once. Returns ``(y, stream')``; ``y`` is None without
-    ``weight``. ``in_place``: ``stream'`` overwrites ``stream``."""
+    ``weight``. ``in_place``: ``stream'`` overwrites ``stream``. ``wide``: the normed rows also unrounded, in
+    float32: returns ``(y, y32, stream')``."""
     _cuda(stream, x, weight, rows_add, vec_add)
     ref = x if x is not None else (rows_add if rows_add is not None else stream)
     if ref is None:
@@ -343,9 +344,13 @@ def stream32_add_norm(stream: torch.Tensor | None, x: torch.Tensor | None, weigh
     if store not in (torch.float32, torch.bfloat16):
         raise KernelError(f"storage type {store} is not built (float32 and bfloat16 are)")
     code = F32 if store == torch.float32 else BF16
+    y32 = None
+    if wide and w is not None:
+        y32 = y if store == torch.float32 else torch.empty(rows, width, dtype=torch.float32, device=ref.device)
     _lib.call("tk_stream32_add_norm", _ptr(stream), _ptr(x), x.stride(0) if x is not None else 0, _ptr(rows_add),
-              _ptr(v), _ptr(w), float(eps), _ptr(out), _ptr(y), rows, width, code, _stream())
-    return y, out
+              _ptr(v), _ptr(w), float(eps), _ptr(out), _ptr(y), _ptr(y32) if y32 is not y else None, rows, width, code,
+              _stream())
+    return (y, y32, out) if wide else (y, out)
 
 
 def glu_clamped(gu: torch.Tensor, limit: float | None, alpha: float, shift: float, block: int = 0) -> torch.Tensor:
@@ -1139,3 +1144,165 @@ def relu2(x: torch.Tensor) -> torch.Tensor:
         raise KernelError("relu2: x must be contiguous")
     _lib.call("tk_relu2", _ptr(x), x.numel(), _dtype_code(x), _stream())
     return x
+
+
+# ---- sequence convolutions, pointwise-weight attention, recurrent state updates ----------------------
+
+SEQ_CONV_MAX_TAPS = 8
+MATRIX_MEMORY_MAX_DIM = 256
+
+
+def scale_rows_f32(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """``float32(x) * scale`` as a new float32 tensor (rows of a 16-bit table that start a 32-bit
+    stream: the product is not rounded to the table's type)."""
+    _cuda(x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("scale_rows_f32: x is [rows, width] with contiguous columns")
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    _lib.call("tk_scale_rows_f32", _ptr(x), x.stride(0), _ptr(out), float(scale), x.shape[0], x.shape[1],
+              _dtype_code(x), _stream())
+    return out
+
+
+def seq_conv(u: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor | None,
+             cu_seqlens: torch.Tensor, seq_ctx: torch.Tensor, seq_slot: torch.Tensor, tiles: tuple,
+             out_dtype: torch.dtype, residual: bool = False, plain: bool = False, out_channels: int | None = None,
+             kv: tuple | None = None):
+    """Causal convolution over time on each channel: ``y_t = [u_t +] bias + sum_j taps[:, j] u_(t - K + 1 + j)``
+    within each sequence (zeros before its start). ``u`` [T, C] (rows may be strided), ``taps`` float32
+    [C, K]; the last K - 1 rows of ``u`` of every sequence are kept in ``state`` (float32
+    [slots, K - 1, C]). ``tiles``: ``ctx.tiles(size)`` with size >= K - 1. ``plain``: also returns ``u``
+    itself in ``out_dtype``. ``kv`` = ``(pool, block_table, page, kv_heads, k_dim, v_dim)``: the
+    channels from ``out_channels`` on are ``kv_heads`` key heads then as many value heads and go into
+    the paged pool at each token's position instead of the result."""
+    _cuda(u, taps, bias, state, cu_seqlens, seq_ctx, seq_slot, *tiles)
+    T, C = u.shape
+    K = taps.shape[1]
+    if u.stride(1) != 1 or taps.dtype != torch.float32 or not taps.is_contiguous() or taps.shape[0] != C:
+        raise KernelError(f"seq_conv: u [T, {C}] with contiguous columns against float32 taps [{C}, K]")
+    if K > 1 and (state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (K - 1, C)
+                  or not state.is_contiguous()):
+        raise KernelError(f"seq_conv: the state is float32 [slots, {K - 1}, {C}]")
+    b = _f32vec(bias, "conv bias", C)
+    n_out = C if out_channels is None else int(out_channels)
+    seq, tok0, off, n = tiles
+    out = torch.empty(T, n_out, dtype=out_dtype, device=u.device) if n_out else None
+    same = torch.empty(T, n_out, dtype=out_dtype, device=u.device) if plain and n_out else None
+    pool = table = None
+    P = hkv = dk = dv = dp = bt = 0
+    if kv is not None:
+        pool, table, P, hkv, dk, dv = kv
+        _cuda(pool, table)
+        if pool.dtype != out_dtype or not pool.is_contiguous() or pool.dim() != 5 or pool.shape[1] != 2 \
+                or pool.shape[2] != hkv or pool.shape[3] != P:
+            raise KernelError(f"seq_conv: the pool is {out_dtype} [pages, 2, {hkv}, {P}, row]")
+        dp, bt = pool.shape[4], _i32(table, "block_table").stride(0)
+    elif n_out != C:
+        raise KernelError("seq_conv: channels beyond the output need a key/value pool")
+    code = {torch.float32: F32, torch.bfloat16: BF16}
+    _lib.call("tk_seq_conv", _ptr(u), u.stride(0), _dtype_code(u), _ptr(taps), _ptr(b), _ptr(state),
+              _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")),
+              _ptr(_i32(seq, "tile_seq")), _ptr(_i32(tok0, "tile_tok0")), _ptr(_i32(off, "tile_off")),
+              _ptr(_i32(n, "tile_n")), seq.numel(), _ptr(out), n_out, _ptr(same), n_out, code[out_dtype], K, C,
+              int(bool(residual)), n_out, _ptr(pool), _ptr(table), bt, int(P), int(hkv), int(dk), int(dv), int(dp),
+              _stream())
+    return (out, same) if plain else out
+
+
+def attention_pointwise_rows() -> int:
+    return _lib.call("tk_attn_pointwise_rows")
+
+
+def attention_pointwise(q: torch.Tensor, kv_pool: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor,
+                        block_table: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
+                        tokens_per_tile: int, window: int | None, scale: float, v_dim: int, cap: float = 0.0,
+                        temp_coef: float = 0.0, temp_every: int = 0, r1: torch.Tensor | None = None,
+                        r2: torch.Tensor | None = None, head_bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention with a weight per visible key instead of a softmax: ``w = sigmoid(s + head_bias[h])``
+    with ``s = cap * tanh(q.k * scale * temp(i) / cap) - r1[h] * ln(1 + r2[h] * (i - j))`` and
+    ``temp(i) = 1 + temp_coef * ln(floor((i + 1) / temp_every) + 1)``; ``out = sum_j w_j v_j``. ``q``
+    [T, H, D], ``kv_pool`` [pages, 2, Hkv, P, row]; returns [T, H, v_dim]. The CUDA-core form: any
+    sizes, both storage types, 32-bit scores, weights and sums."""
+    _cuda(q, kv_pool)
+    T, H, D = q.shape
+    _, two, Hkv, P, Dp = kv_pool.shape
+    if two != 2 or kv_pool.dtype != q.dtype or Dp < max(D, v_dim) or not (q.is_contiguous() and kv_pool.is_contiguous()):
+        raise KernelError("attention_pointwise: q [T, H, D] and a cache [pages, 2, Hkv, P, >= D] of one type expected")
+    for name, t in (("r1", r1), ("r2", r2), ("head_bias", head_bias)):
+        _f32vec(t, name, H)
+    out = torch.empty(T, H, v_dim, dtype=q.dtype, device=q.device)
+    _lib.call("tk_attn_pointwise", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
+              _ptr(_i32(tile_tok0, "tile_tok0")), _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(),
+              int(tokens_per_tile), H, Hkv, D, int(v_dim), Dp, P, int(window or 0), float(scale), float(cap or 0.0),
+              float(temp_coef or 0.0), int(temp_every or 0), _ptr(r1), _ptr(r2), _ptr(head_bias), _dtype_code(q),
+              _stream())
+    return out
+
+
+def rglru_scan(z: torch.Tensor, rb: torch.Tensor, ib: torch.Tensor, decay: torch.Tensor, u: torch.Tensor,
+               y: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, seq_ctx: torch.Tensor,
+               seq_slot: torch.Tensor, n_seqs: int) -> torch.Tensor:
+    """``S_t = a S_(t-1) + sqrt(1 - a^2) i u_t`` per channel with ``a = exp(decay * sigmoid(zr + rb))``,
+    ``i = sigmoid(zi + ib)``; returns ``S_t * gelu_tanh(y_t)`` [T, W] in the type of ``u``. ``z`` float32
+    [blocks, T, 2 w] (each block's recurrence-gate then input-gate products), ``u`` / ``y`` [T, W] (rows
+    may be strided), ``state`` float32 [slots, W]."""
+    _cuda(z, rb, ib, decay, u, y, state)
+    blocks, Tz, w2 = z.shape
+    T, W = u.shape
+    if z.dtype != torch.float32 or not z.is_contiguous() or Tz != T or blocks * w2 != 2 * W:
+        raise KernelError(f"rglru_scan: z is float32 [blocks, {T}, 2 w] with blocks * w = {W}")
+    if u.stride(1) != 1 or y.stride(1) != 1 or y.dtype != u.dtype or y.shape[0] != T or y.shape[1] != W:
+        raise KernelError("rglru_scan: u and y are [T, W] of one type with contiguous columns")
+    if state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1] != W:
+        raise KernelError(f"rglru_scan: the state is float32 [slots, {W}]")
+    out = torch.empty(T, W, dtype=u.dtype, device=u.device)
+    _lib.call("tk_rglru_scan", _ptr(z), T, _ptr(_f32vec(rb, "rb", W)), _ptr(_f32vec(ib, "ib", W)),
+              _ptr(_f32vec(decay, "decay", W)), _ptr(u), u.stride(0), _ptr(y), y.stride(0), _ptr(state),
+              _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")),
+              int(n_seqs), _ptr(out), W, blocks, _dtype_code(u), _stream())
+    return out
+
+
+def mlstm_scan(qkv: torch.Tensor, offsets: tuple, gates: torch.Tensor, cap: float, q_scale: float,
+               S_state: torch.Tensor, m_state: torch.Tensor, cu_seqlens: torch.Tensor, seq_ctx: torch.Tensor,
+               seq_slot: torch.Tensor, n_seqs: int, heads: int, dim: int, v_dim: int):
+    """The matrix memory's recurrence over a step's tokens. ``qkv`` [T, *]: q (heads x dim) at column
+    ``offsets[0]``, k at ``offsets[1]``, v (heads x v_dim) at ``offsets[2]``; ``gates`` float32 [T, >= 2
+    heads]: input- then forget-gate pre-activations. ``S_state`` float32 [slots, heads, v_dim + 1, dim]
+    (the last column is n), ``m_state`` float32 [slots, heads]. Returns ``num`` float32 [T, heads,
+    v_dim + 1] (``S_t^T q_t``; the last column ``n_t . q_t``) and ``m`` float32 [T, heads];
+    ``mlstm_norm_gate`` finishes the output and commits ``m``."""
+    _cuda(qkv, gates, S_state, m_state)
+    T = qkv.shape[0]
+    if qkv.stride(1) != 1 or gates.dtype != torch.float32 or gates.stride(1) != 1 or gates.shape[1] < 2 * heads:
+        raise KernelError("mlstm_scan: qkv with contiguous columns, gates float32 [T, >= 2 heads]")
+    if (S_state.dtype != torch.float32 or tuple(S_state.shape[1:]) != (heads, v_dim + 1, dim) or not S_state.is_contiguous()
+            or m_state.dtype != torch.float32 or tuple(m_state.shape[1:]) != (heads,) or not m_state.is_contiguous()):
+        raise KernelError(f"mlstm_scan: states float32 [slots, {heads}, {v_dim + 1}, {dim}] and [slots, {heads}]")
+    num = torch.empty(T, heads, v_dim + 1, dtype=torch.float32, device=qkv.device)
+    m = torch.empty(T, heads, dtype=torch.float32, device=qkv.device)
+    _lib.call("tk_mlstm_scan", _ptr(qkv), qkv.stride(0), int(offsets[0]), int(offsets[1]), int(offsets[2]), _ptr(gates),
+              gates.stride(0), float(cap or 0.0), float(q_scale), _ptr(S_state), _ptr(m_state),
+              _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")),
+              int(n_seqs), _ptr(num), _ptr(m), heads, dim, v_dim, _dtype_code(qkv), _stream())
+    return num, m
+
+
+def mlstm_norm_gate(num: torch.Tensor, m: torch.Tensor, m_state: torch.Tensor, weight: torch.Tensor,
+                    gate: torch.Tensor | None, tok_seq: torch.Tensor, cu_seqlens: torch.Tensor,
+                    seq_slot: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``o = num[..., :-1] / (max(|num[..., -1]|, exp(-m)) + 1e-6)``, each head divided by its root mean
+    square, times ``weight`` [heads * v_dim], times ``sigmoid(gate)`` [T, heads * v_dim] (rows may be
+    strided); returns [T, heads * v_dim]. The last token of each sequence writes its ``m`` to ``m_state``."""
+    _cuda(num, m, m_state, weight, gate)
+    T, H, cols = num.shape
+    vd = cols - 1
+    if gate is not None and (gate.dtype != out_dtype or gate.stride(1) != 1 or gate.shape[1] != H * vd):
+        raise KernelError(f"mlstm_norm_gate: the gate is {out_dtype} [T, {H * vd}] with contiguous columns")
+    out = torch.empty(T, H * vd, dtype=out_dtype, device=num.device)
+    _lib.call("tk_mlstm_norm_gate", _ptr(num), _ptr(m), _ptr(m_state), _ptr(_f32vec(weight, "norm weight", H * vd)),
+              _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(_i32(tok_seq, "tok_seq")),
+              _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_slot, "seq_slot")), _ptr(out), T, H, vd, float(eps),
+              F32 if out_dtype == torch.float32 else BF16, _stream())
+    return out

@@ -37,7 +37,7 @@ _SIGNATURES = {
     "tk_attn_generic_rows": [],
     "tk_attn_generic": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P],
     "tk_rotary_write": [P, L, P, P, P, F, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P],
-    "tk_stream32_add_norm": [P, P, L, P, P, P, F, P, P, I, I, I, P],
+    "tk_stream32_add_norm": [P, P, L, P, P, P, F, P, P, P, I, I, I, P],
     "tk_glu_clamped": [P, P, I, I, I, F, F, F, I, P],
     "tk_gemm_skinny_glu": [P, L, P, L, P, P, L, I, I, I, I, F, F, F, P],
     "tk_sigmoid_gate": [P, P, L, I, I, I, P],
@@ -89,6 +89,13 @@ _SIGNATURES = {
     "tk_gemm_grouped_mma": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, I, P, L, P],
     "tk_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
     "tk_relu2": [P, L, I, P],
+    "tk_scale_rows_f32": [P, L, P, F, I, I, I, P],
+    "tk_seq_conv": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, P, L, P, L, I, I, I, I, I, P, P, I, I, I, I, I, I, P],
+    "tk_attn_pointwise_rows": [],
+    "tk_attn_pointwise": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, F, I, P, P, P, I, P],
+    "tk_rglru_scan": [P, I, P, P, P, P, L, P, L, P, P, P, P, I, P, I, I, I, P],
+    "tk_mlstm_scan": [P, L, I, I, I, P, L, F, F, P, P, P, P, P, I, P, P, I, I, I, I, P],
+    "tk_mlstm_norm_gate": [P, P, P, P, P, L, P, P, P, P, I, I, I, F, I, P],
 }
 
 
@@ -139,7 +146,7 @@ _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled"
             "tk_attn_mma_supported", "tk_attn_decode_fused_supported", "tk_attn_decode_fused_max_splits", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
             "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status",
             "tk_attn_latent_rows", "tk_attn_latent_max_rank", "tk_gemm_grouped_tile", "tk_attn_latent_mma_rows",
-            "tk_attn_latent_mma_supported"}
+            "tk_attn_latent_mma_supported", "tk_attn_pointwise_rows"}
 
 
 _fns: dict = {}

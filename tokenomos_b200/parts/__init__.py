@@ -1,8 +1,8 @@
 """Parts a model is put together from: mixers, feed-forwards, norms, position encodings, block
 arrangements; ``build_model`` turns a ``ModelSpec`` and its tensors into a runnable ``Stack``."""
 
-from tokenomos_b200.parts import (attention, block, embedding, ffn, hyper, latent, moe, norm, rope,  # noqa: F401
-                                  shortconv)                                                       # (register)
+from tokenomos_b200.parts import (attention, block, convpos, embedding, ffn, hyper, latent, moe, norm,  # noqa: F401
+                                  parallel, recurrent, rope, shortconv)                                                     # (register)
 from tokenomos_b200.parts.build import build_model
 from tokenomos_b200.parts.registry import Runtime, register
 

@@ -13,12 +13,17 @@ window: the first positions of a sequence stay visible, at their true positions)
 (value heads of another size than the keys); ``v_is_k`` (no value projection: a key as projected,
 before the position encoding, is its value); ``gate_kind`` "element" (the gate has one value
 per output element, not per head); ``exact`` (the softmax's weights stay 32-bit until they meet
-the values in kernels that do not need them in 16 bits).
+the values in kernels that do not need them in 16 bits); ``pointwise`` (no softmax: every visible
+key has the weight ``sigmoid(s + bias[h])`` of its own score, with an optional cap ``c tanh(s / c)``,
+a bias by distance ``- r1[h] ln(1 + r2[h] (i - j))`` and a query temperature ``1 + coef ln(floor((i + 1)
+/ every) + 1)``; ``PointwiseWeights``). A position part may keep state per request (a short
+convolution on q, k and v): it then has ``state_specs()`` and is called with the layer's ``call``.
 """
 
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass
 
 import torch
 
@@ -28,6 +33,19 @@ from tokenomos_b200.parts.linear import Linear
 from tokenomos_b200.parts.registry import DEFAULT_TUNING, Runtime, Tuning, builder_of, register
 
 
+@dataclass(frozen=True)
+class PointwiseWeights:
+    """Weights that are not a softmax (see the module's head). ``cap`` 0: none; ``temp_every`` 0: no
+    temperature; ``r1`` / ``r2`` / ``head_bias``: float32 [heads] or None."""
+
+    cap: float = 0.0
+    temp_coef: float = 0.0
+    temp_every: int = 0
+    r1: torch.Tensor | None = None
+    r2: torch.Tensor | None = None
+    head_bias: torch.Tensor | None = None
+
+
 class Attention:
     def __init__(self, qkv: Linear, o: Linear, heads: int, kv_heads: int, head_dim: int, rope,
                  eps: float, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
@@ -35,7 +53,7 @@ class Attention:
                  gate: Linear | None = None, kv_source: int | None = None,
                  gate_fused: bool = False, tuning: Tuning = DEFAULT_TUNING, sink: bool = False,
                  keep_first: int = 0, v_dim: int | None = None, v_is_k: bool = False,
-                 gate_kind: str = "head", exact: bool = False):
+                 gate_kind: str = "head", exact: bool = False, pointwise: PointwiseWeights | None = None):
         """``gate``: the per-head gate's projection as a part of its own; ``gate_fused``: its rows
         are the last of ``qkv``'s instead (after q, k, v, then zero rows up to a multiple of 8), so
         that one product yields both."""
@@ -48,11 +66,14 @@ class Attention:
             raise ValueError("attention: kept first positions need a window")
         self.sink, self.keep_first, self.v_dim, self.v_is_k = bool(sink), int(keep_first), v_dim, bool(v_is_k)
         self.gate_kind, self.exact = gate_kind, bool(exact)
+        self.pointwise = pointwise
+        if pointwise is not None and (sink or keep_first):
+            raise ValueError("attention: a sink and kept first positions belong to the softmax")
         # what the one-kernel decode form and the norms folded into the projections do not take
         # (the tensor-core kernels take all of it but a value size of its own; the general
         # kernel takes everything)
         self.extended = bool(self.sink or self.keep_first or self.v_is_k or v_dim != head_dim
-                             or gate_kind != "head" or self.exact)
+                             or gate_kind != "head" or self.exact or pointwise is not None)
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads over {kv_heads} KV heads")
         if head_dim > ops.ATTENTION_MAX_HEAD_DIM:
@@ -89,12 +110,14 @@ class Attention:
                                       v_dim=v_dim, v_is_k=self.v_is_k)
 
     def state_specs(self) -> dict:
+        # a position part with state of its own per request lists it (under names of its own)
+        more = self.rope.state_specs(self.head_layout) if hasattr(self.rope, "state_specs") else {}
         if self.kv_source is not None:
-            return {"kv": SharedState(self.kv_source, "kv")}
+            return {"kv": SharedState(self.kv_source, "kv"), **more}
         row = max(self.head_dim, self.v_dim)         # a cache row holds a key or a value
         if self.window is None:
-            return {"kv": PagedKV(self.kv_heads, row)}
-        return {"kv": WindowKV(self.kv_heads, row, self.window, self.keep_first)}
+            return {"kv": PagedKV(self.kv_heads, row), **more}
+        return {"kv": WindowKV(self.kv_heads, row, self.window, self.keep_first), **more}
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T = x.shape[0]
@@ -188,8 +211,19 @@ class Attention:
         pool = ctx.states[(call, "kv")]
         table = ctx.block_tables[ctx.state_groups[(call, "kv")]]
         own_kv = self.head_layout.kv_heads
-        q = self.rope.encode_qk(qkv, ctx, self.head_layout, pool if own_kv else None,
-                                table if own_kv else None)
+        if hasattr(self.rope, "state_specs"):
+            q = self.rope.encode_qk(qkv, ctx, self.head_layout, pool if own_kv else None,
+                                    table if own_kv else None, call=call)
+        else:
+            q = self.rope.encode_qk(qkv, ctx, self.head_layout, pool if own_kv else None,
+                                    table if own_kv else None)
+        if self.pointwise is not None:
+            out = self._attend_pointwise(q, pool, table, ctx)
+            if gate is not None and self.gate_kind == "head":
+                ops.head_gate(out, gate, self.heads, self.v_dim)
+            elif gate is not None:
+                ops.sigmoid_gate(out, gate)
+            return out
         # the tensor-core kernels take everything but value heads of another size than the keys
         if self.v_dim == self.head_dim and ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim,
                                                                        q.dtype):
@@ -206,6 +240,17 @@ class Attention:
         elif gate is not None:
             ops.sigmoid_gate(out, gate)
         return out
+
+    def _attend_pointwise(self, q, pool, table, ctx: StepContext) -> torch.Tensor:
+        """Weights of their own per key (no softmax): the CUDA-core kernel."""
+        w = self.pointwise
+        rows = ops.attention_pointwise_rows()
+        group = self.heads // self.kv_heads
+        per_tile = max(1, rows // group)
+        _, tok0, _, ntok = ctx.tiles(per_tile)
+        return ops.attention_pointwise(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile, self.window,
+                                       self.scale, self.v_dim, w.cap, w.temp_coef, w.temp_every, w.r1, w.r2,
+                                       w.head_bias)
 
     # whether prompt portions may take the tcgen05 kernel (TOKENOMOS_B200_ATTN_TC=0: never)
     prefill_tc = os.environ.get("TOKENOMOS_B200_ATTN_TC", "1") != "0"
@@ -285,6 +330,20 @@ class Attention:
         return out
 
 
+def _pointwise(params: dict | None, tensors: dict) -> PointwiseWeights | None:
+    """``params``: ``cap``, ``temp_coef``, ``temp_every`` (each optional); tensors ``dist_r1``, ``dist_r2``,
+    ``head_bias`` (float32 [heads], each optional)."""
+    if params is None:
+        return None
+
+    def vec(name):
+        t = tensors.get(name)
+        return t.float().contiguous() if t is not None else None
+
+    return PointwiseWeights(float(params.get("cap") or 0.0), float(params.get("temp_coef") or 0.0),
+                            int(params.get("temp_every") or 0), vec("dist_r1"), vec("dist_r2"), vec("head_bias"))
+
+
 @register("mixer", "attention")
 def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
     rope_spec = params["position"]
@@ -317,4 +376,5 @@ def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
         tensors.get("k_norm"), params.get("window"), params.get("scale"), None, source,
         gate_fused=gated, tuning=rt.tuning, sink=params.get("sink", False),
         keep_first=params.get("keep_first", 0), v_dim=params.get("v_dim"), v_is_k=v_is_k,
-        gate_kind=params.get("gate_kind", "head"), exact=params.get("exact", False))
+        gate_kind=params.get("gate_kind", "head"), exact=params.get("exact", False),
+        pointwise=_pointwise(params.get("pointwise"), tensors))

@@ -92,8 +92,11 @@ class Stack:
     def __init__(self, embedding: torch.Tensor, blocks: list, order: list[LayerCall], final_norm,
                  head: Linear | None, tuning: Tuning = DEFAULT_TUNING, embed_scale: float | None = None,
                  logit_softcap: float | None = None, suppress: tuple[int, ...] = (),
-                 extras: dict[str, torch.Tensor] | None = None, embedder=None):
+                 extras: dict[str, torch.Tensor] | None = None, embedder=None, embed_wide: bool = False):
         self.embedding = embedding
+        # the scaled embedding rows start a 32-bit stream unrounded (else they are rounded to the
+        # storage type, as a 16-bit stream would hold them)
+        self.embed_wide = bool(embed_wide)
         self.embedder = embedder
         self.extras = {name: t.float().contiguous() for name, t in (extras or {}).items()}
         self.embed_scale = None if embed_scale is None else float(embed_scale)
@@ -165,7 +168,11 @@ class Stack:
     def embed(self, ids: torch.Tensor, ctx: StepContext | None = None) -> torch.Tensor:
         if self.embedder is not None:
             return self.embedder.forward(ids, ctx)
-        h = ops.gather_rows(self.embedding, ids)
+        return self._scaled(ops.gather_rows(self.embedding, ids))
+
+    def _scaled(self, h: torch.Tensor) -> torch.Tensor:
+        if self.embed_wide:
+            return ops.scale_rows_f32(h, 1.0 if self.embed_scale is None else self.embed_scale)
         return h if self.embed_scale is None else ops.scale_rows(h, self.embed_scale)
 
     def embed_fed(self, ids_host: torch.Tensor, use_prev: torch.Tensor, last_token: torch.Tensor,
@@ -174,8 +181,7 @@ class Stack:
         ``last_token[slot[r]]`` where ``use_prev[r]`` is set, else ``ids_host[r]``."""
         if self.embedder is not None:
             return self.embedder.forward(ids_host, ctx, (use_prev, last_token, slot))
-        h = ops.gather_rows_select(self.embedding, ids_host, use_prev, last_token, slot)
-        return h if self.embed_scale is None else ops.scale_rows(h, self.embed_scale)
+        return self._scaled(ops.gather_rows_select(self.embedding, ids_host, use_prev, last_token, slot))
 
     def forward(self, h: torch.Tensor, ctx: StepContext):
         """Runs the layer list; returns ``(h, residual, pending)`` of the last block: the final
@@ -210,6 +216,8 @@ class Stack:
             h = ops.gather_rows(h, rows)
             if residual is not None:
                 residual = ops.gather_rows(residual, rows)
+            if hasattr(pending, "gather"):       # rows of its own that still join the stream
+                pending = pending.gather(rows)
         y, _ = self.final_norm.add_norm(h, residual, pending)
         out = self.head(y, out_dtype=torch.float32)
         if self.logit_softcap is not None or self.suppress is not None:

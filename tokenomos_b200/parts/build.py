@@ -46,4 +46,5 @@ def build_model(spec: ModelSpec, tensors: dict, rt: Runtime) -> Stack:
     embedder = _part("embedding", spec.embedder, tensors, rt) if spec.embedder is not None else None
     return Stack(tensors[spec.embedding.name], blocks, list(spec.order), final_norm, head,
                  tuning=rt.tuning, embed_scale=spec.embed_scale, logit_softcap=spec.logit_softcap,
-                 suppress=spec.suppress, extras=extras, embedder=embedder)
+                 suppress=spec.suppress, extras=extras, embedder=embedder,
+                 embed_wide=spec.embed_wide)

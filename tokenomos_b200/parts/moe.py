@@ -28,11 +28,18 @@ class RoutedExperts:
 
     def __init__(self, router: Linear, up: torch.Tensor, down: torch.Tensor, top: int, scale: float,
                  shared_up: Linear | None = None, shared_down: Linear | None = None, shared_gate: bool = False,
-                 library_rows: int = 1024):
+                 library_rows: int = 1024, activation: str = "relu2"):
         """``up`` [E, ff, width], ``down`` [E, width, ff]; ``router`` [E (+ 1 if ``shared_gate``) (+ zero
-        rows), width]."""
+        rows), width] (it may carry a bias). ``activation`` "relu2": ``act(v) = relu(v)^2``; "swiglu": an
+        expert is ``W_down (silu(W_gate h) * (W_up h))`` and ``up`` holds each expert's gate rows, then its
+        up rows ([E, 2 ff, width])."""
+        if activation not in ("relu2", "swiglu"):
+            raise ValueError(f"mixture of experts: activation {activation!r}: 'relu2' or 'swiglu'")
+        self.activation = activation
         self.router, self.up, self.down = router, up.contiguous(), down.contiguous()
         self.experts, self.ff, self.width = up.shape
+        if activation == "swiglu":
+            self.ff //= 2
         self.top, self.scale = int(top), float(scale)
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"mixture of experts: {self.top} of {self.experts} experts per token")
@@ -46,6 +53,8 @@ class RoutedExperts:
         self.library_rows = int(library_rows)
         self.library = (hasattr(torch, "_grouped_mm") and up.dtype == torch.bfloat16 and self.ff % 8 == 0
                         and self.width % 8 == 0)
+        # (the tiles of both products: the common divisor of their sizes stands for both)
+        self._tile_n = math.gcd(self.up.shape[1], self.width)
         if router.out_features < self.experts + (1 if shared_gate else 0):
             raise ValueError("mixture of experts: the router does not match the expert count")
 
@@ -56,11 +65,14 @@ class RoutedExperts:
             y, pair_row = self._experts_library(x, idx)
             return ops.moe_combine(y, pair_row, w, self._shared(x), gate)
         # (both products, [ff, width] and [width, ff], must take the tile: the common divisor stands for both sizes)
-        tile = ops.gemm_grouped_tiles(x.dtype, math.gcd(self.ff, self.width), math.gcd(self.ff, self.width),
+        tile = ops.gemm_grouped_tiles(x.dtype, math.gcd(self._tile_n, self.ff), math.gcd(self._tile_n, self.ff),
                                       x.shape[0] * self.top)
         row_token, pair_row, tile_expert = ops.moe_sort(idx, self.experts, tile)
         rows = row_token.numel()
-        act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act=True, tile=tile)
+        if self.activation == "swiglu":
+            act = ops.swiglu(ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, tile=tile))
+        else:
+            act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act=True, tile=tile)
         y = ops.gemm_grouped(act, self.down, tile_expert, None, rows, tile=tile)
         return ops.moe_combine(y, pair_row, w, self._shared(x), gate)
 
@@ -74,7 +86,8 @@ class RoutedExperts:
         layout, each expert's block of rows given by its end."""
         row_token, pair_row, _, ends = ops.moe_sort(idx, self.experts, 8, ends=True)
         rows = ops.gather_rows_or_zero(x, row_token)
-        act = ops.relu2(torch._grouped_mm(rows, self.up.transpose(1, 2), offs=ends))
+        act = torch._grouped_mm(rows, self.up.transpose(1, 2), offs=ends)
+        act = ops.swiglu(act) if self.activation == "swiglu" else ops.relu2(act)
         return torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends), pair_row
 
 
@@ -98,3 +111,22 @@ def build_routed_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExpe
     shared_down = Linear(tensors["shared_down"], tuning=rt.tuning) if "shared_down" in tensors else None
     return RoutedExperts(router, up, down, params["top"], params["scale"], shared_up, shared_down, gate is not None,
                          library_rows=rt.tuning.grouped_library_rows)
+
+
+@register("feed_forward", "swiglu_moe")
+def build_gated_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExperts:
+    """Experts ``W_down (silu(W_gate h) * (W_up h))``; router logits ``W_r h + b`` in 32-bit; the weights
+    of the ``top`` experts with the largest logits are the softmax over those logits alone (which is the
+    softmax over all of them, renormalised over the chosen)."""
+    n = params["experts"]
+    up = torch.stack([torch.cat((tensors[f"e{i}.gate"], tensors[f"e{i}.up"])) for i in range(n)])
+    down = torch.stack([tensors[f"e{i}.down"] for i in range(n)])
+    w = tensors["router"].to(rt.dtype)
+    bias = tensors.get("router_bias")
+    pad = -n % 8
+    if pad:
+        w = torch.cat((w, w.new_zeros(pad, w.shape[1])))
+        if bias is not None:
+            bias = torch.cat((bias.float(), torch.zeros(pad, dtype=torch.float32, device=bias.device)))
+    return RoutedExperts(Linear(w, bias, tuning=rt.tuning), up, down, params["top"], params.get("scale", 1.0),
+                         library_rows=rt.tuning.grouped_library_rows, activation="swiglu")

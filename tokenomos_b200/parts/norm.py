@@ -44,6 +44,18 @@ def build_rmsnorm(params: dict, tensors: dict, rt: Runtime) -> RMSNorm:
     return RMSNorm(tensors["weight"], params["eps"])
 
 
+class PendingAdd:
+    """Rows that still have to join the residual stream beside a block's output: an arrangement
+    whose sublayers run side by side hands the second sublayer's output on this way, and the next
+    norm's kernel adds both in 32-bit. ``gather`` keeps the rows a list of indices names."""
+
+    def __init__(self, rows: torch.Tensor):
+        self.rows = rows
+
+    def gather(self, index: torch.Tensor) -> "PendingAdd":
+        return PendingAdd(ops.gather_rows(self.rows, index))
+
+
 class StreamNorm32:
     """RMSNorm over a residual stream that is kept in 32-bit whatever the model's storage type.
 
@@ -63,14 +75,18 @@ class StreamNorm32:
         self.width = weight.numel()
         self.store = store
 
-    def add_norm(self, x: torch.Tensor, residual: torch.Tensor | None, pre=None):
-        """``stream = residual + x``; returns ``(norm(stream), stream)``. ``x`` alone may be the
-        stream itself (float32 in a 16-bit model) or the rows that start one."""
-        if pre is not None:
+    def add_norm(self, x: torch.Tensor, residual: torch.Tensor | None, pre=None, wide: bool = False):
+        """``stream = residual + x (+ pre.rows)``; returns ``(norm(stream), stream)``. ``x`` alone may
+        be the stream itself (float32 in a 16-bit model) or the rows that start one. ``pre``: a
+        ``PendingAdd`` or None (no post-norm can be taken into the add). ``wide``: the normed rows
+        also unrounded: returns ``(norm(stream), the same in float32, stream)``."""
+        if pre is not None and not isinstance(pre, PendingAdd):
             raise ValueError("StreamNorm32: no post-norm can be taken into the add")
-        if residual is None and x.dtype == torch.float32 and self.store != torch.float32:
-            return ops.stream32_add_norm(x, None, self.weight, self.eps, out_dtype=self.store, in_place=True)
-        return ops.stream32_add_norm(residual, x, self.weight, self.eps, out_dtype=self.store)
+        more = pre.rows if pre is not None else None
+        if residual is None and x.dtype == torch.float32 and (self.store != torch.float32 or more is not None):
+            return ops.stream32_add_norm(x, None, self.weight, self.eps, rows_add=more, out_dtype=self.store,
+                                         in_place=True, wide=wide)
+        return ops.stream32_add_norm(residual, x, self.weight, self.eps, rows_add=more, out_dtype=self.store, wide=wide)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         return self.add_norm(x, None)[0]
@@ -78,4 +94,9 @@ class StreamNorm32:
 
 @register("norm", "rmsnorm32")
 def build_stream_norm32(params: dict, tensors: dict, rt: Runtime) -> StreamNorm32:
-    return StreamNorm32(tensors["weight"], params["eps"], params.get("offset", 0.0), rt.dtype)
+    norm = StreamNorm32(tensors["weight"], params["eps"], params.get("offset", 0.0), rt.dtype)
+    # taps of a convolution on what a sublayer behind this norm reads (``parts.parallel``): the
+    # arrangement that has one finds them here
+    norm.input_taps = tensors.get("taps")
+    norm.conv_tile = rt.tuning.conv_tile
+    return norm

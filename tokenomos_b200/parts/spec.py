@@ -94,6 +94,8 @@ class ModelSpec:
     # the embedding rows times a constant (rounded to the work type, as is the product); the
     # logits through ``cap * tanh(logits / cap)``; token ids whose logits are -inf
     embed_scale: float | None = None
+    # the scaled rows are kept in 32-bit (they start a 32-bit residual stream unrounded)
+    embed_wide: bool = False
     logit_softcap: float | None = None
     suppress: tuple[int, ...] = ()
     # tensors of the stack itself (not of a block), by the name ``StreamAdd.tensor`` uses
