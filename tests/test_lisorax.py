@@ -480,6 +480,86 @@ def test_attention_mixer_alone(case, how, dtype, tmp_path):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("H, G, D, page", [(4, 2, 64, 16), (6, 1, 64, 8), (2, 2, 128, 32), (16, 1, 128, 12)])
+def test_tensor_core_pointwise_attention_against_the_plain_weights(H, G, D, page, window):
+    """The tensor-core kernels alone over a pool of random keys and values in shuffled pages: prompt
+    portions that start in the middle of a page and of a 64-key tile, single tokens at position 0 and
+    far out shared 1, 3 and 7 ways over their keys, unused (negative) entries in the list of single
+    tokens, with and without a window."""
+    from tokenomos_b200 import ops
+
+    g = torch.Generator().manual_seed(H * 100 + D + page)
+    seqs = [(100, 70), (299, 1), (0, 1), (0, 17), (63, 2), (640, 1)]          # (cached, new) per sequence
+    width = max(-(-(c + n) // page) for c, n in seqs)
+    n_pages = 1 + sum(-(-(c + n) // page) for c, n in seqs)
+    order = (1 + torch.randperm(n_pages - 1, generator=g)).tolist()
+    table = torch.zeros(len(seqs), width, dtype=torch.int32)
+    pool = torch.full((n_pages, 2, G, page, D), float("nan"))
+    keys, values, positions, tok_seq = [], [], [], []
+    r1, r2, hb = 2.0 * torch.rand(H, generator=g), 0.05 + 0.5 * torch.rand(H, generator=g), -3.0 + torch.randn(H, generator=g)
+    for s, (c, n) in enumerate(seqs):
+        k = torch.randn(c + n, G, D, generator=g).to(torch.bfloat16).float()
+        v = torch.randn(c + n, G, D, generator=g).to(torch.bfloat16).float()
+        for b in range(-(-(c + n) // page)):
+            pg = order.pop()
+            table[s, b] = pg
+            rows = slice(b * page, min(c + n, (b + 1) * page))
+            pool[pg, 0, :, :rows.stop - rows.start] = k[rows].transpose(0, 1)
+            pool[pg, 1, :, :rows.stop - rows.start] = v[rows].transpose(0, 1)
+        keys.append(k)
+        values.append(v)
+        positions += list(range(c, c + n))
+        tok_seq += [s] * n
+    T = len(positions)
+    q = (1.5 * torch.randn(T, H, D, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+    scale, cap, coef, every = 0.6, 11.0, 0.3, 64
+    want = torch.zeros(T, H, D, dtype=torch.float64)
+    for t in range(T):
+        s, i = tok_seq[t], positions[t]
+        lo = 0 if window is None else max(0, i - window + 1)
+        temp = 1 + coef * math.log((i + 1) // every + 1)
+        dist = torch.arange(i - lo, -1, -1, dtype=torch.float64)
+        for h in range(H):
+            kv = h // (H // G)
+            sc = (keys[s][lo:i + 1, kv].double() @ q[t, h].double()) * scale * temp
+            sc = cap * torch.tanh(sc / cap) - r1[h].double() * torch.log(1 + r2[h].double() * dist) + hb[h].double()
+            want[t, h] = torch.sigmoid(sc) @ values[s][lo:i + 1, kv].double()
+    per = ops.attention_pointwise_mma_tokens(H, G)
+    tok0, ntok, singles, first = [], [], [-1], 0
+    for c, n in seqs:
+        if n == 1:
+            singles += [first, -1]
+        else:
+            for a in range(0, n, per):
+                tok0.append(first + a)
+                ntok.append(min(per, n - a))
+        first += n
+    tok0 += [0, 0]
+    ntok += [0, 0]                                # unused entries of a fixed-length tile list
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    args = (dev(positions), dev(tok_seq), table.cuda())
+    vec = [x.float().cuda() for x in (r1, r2, hb)]
+    pool16 = pool.to(torch.bfloat16).cuda()
+    for nsplit in (1, 3, 7):
+        out = torch.full((T, H, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.attention_pointwise_mma(q.cuda(), pool16, out, *args, dev(tok0), dev(ntok), dev(singles), len(singles), nsplit,
+                                    window, scale, cap, coef, every, *vec)
+        err = (out.double().cpu() - want).abs().amax(dim=(1, 2))
+        assert torch.isfinite(out).all() and (err < 1.5e-2 * want.abs().amax()).all(), (nsplit, err.argmax(), err.max())
+    # every row a single token, in order, without a list
+    only = [t for t in range(T) if t == 0 or tok_seq[t] != tok_seq[t - 1]]
+    if only:
+        rows = [t + [n for _, n in seqs][tok_seq[t]] - 1 for t in only]       # each sequence's last token
+        out = torch.zeros(len(rows), H, D, dtype=torch.bfloat16, device="cuda")
+        ops.attention_pointwise_mma(q[rows].contiguous().cuda(), pool16, out, dev([positions[t] for t in rows]),
+                                    dev([tok_seq[t] for t in rows]), table.cuda(), None, None, None, len(rows), 2,
+                                    window, scale, cap, coef, every, *vec)
+        err = (out.double().cpu() - want[rows]).abs().amax(dim=(1, 2))
+        assert (err < 1.5e-2 * want.abs().amax()).all(), err
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("how", ["whole", "decoded", "portions"])
 @pytest.mark.parametrize("conv", [None, 3])

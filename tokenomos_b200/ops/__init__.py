@@ -1240,6 +1240,46 @@ def attention_pointwise(q: torch.Tensor, kv_pool: torch.Tensor, positions: torch
     return out
 
 
+def attention_pointwise_mma_supported(heads: int, kv_heads: int, head_dim: int, v_dim: int, row: int,
+                                      dtype: torch.dtype) -> bool:
+    """Whether the tensor-core form of ``attention_pointwise`` takes the shape (bfloat16, keys, values
+    and cache rows of one size, 64 or 128, at most 16 query heads per key/value head)."""
+    return dtype == torch.bfloat16 and bool(_lib.call("tk_attn_pointwise_mma_supported", heads, kv_heads, head_dim,
+                                                      v_dim, row))
+
+
+def attention_pointwise_mma_tokens(heads: int, kv_heads: int) -> int:
+    """Tokens per tile the tensor-core form expects for prompt portions."""
+    return _lib.call("tk_attn_pointwise_mma_tokens", heads, kv_heads)
+
+
+def attention_pointwise_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                            tok_seq: torch.Tensor, block_table: torch.Tensor, tile_tok0: torch.Tensor | None,
+                            tile_ntok: torch.Tensor | None, singles: torch.Tensor | None, n_single: int, nsplit: int,
+                            window: int | None, scale: float, cap: float = 0.0, temp_coef: float = 0.0,
+                            temp_every: int = 0, r1: torch.Tensor | None = None, r2: torch.Tensor | None = None,
+                            head_bias: torch.Tensor | None = None) -> None:
+    """``attention_pointwise`` on the tensor cores: the tiles of prompt portions (``tile_tok0`` /
+    ``tile_ntok``, ``attention_pointwise_mma_tokens`` tokens each) and ``n_single`` single tokens (their
+    rows in ``singles``; None: rows 0 .. n_single - 1), each shared ``nsplit`` ways over its keys. The
+    32-bit weights are rounded to bfloat16 where they meet the values. Writes those rows of ``out``."""
+    _cuda(q, kv_pool, out, positions, tok_seq, block_table, tile_tok0, tile_ntok, singles)
+    T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_pointwise_mma")
+    for name, t in (("r1", r1), ("r2", r2), ("head_bias", head_bias)):
+        _f32vec(t, name, H)
+    n_tiles = tile_tok0.numel() if tile_tok0 is not None else 0
+    partial = None
+    if n_single and nsplit > 1:
+        partial = torch.empty(nsplit * n_single * H * D, dtype=torch.float32, device=q.device)
+    _lib.call("tk_attn_pointwise_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
+              _ptr(_i32(tile_tok0, "tile_tok0")) if n_tiles else None,
+              _ptr(_i32(tile_ntok, "tile_ntok")) if n_tiles else None, n_tiles,
+              _ptr(_i32(singles, "singles")) if singles is not None else None, int(n_single), int(nsplit),
+              _ptr(partial), H, Hkv, D, P, int(window or 0), float(scale), float(cap or 0.0), float(temp_coef or 0.0),
+              int(temp_every or 0), _ptr(r1), _ptr(r2), _ptr(head_bias), _stream())
+
+
 def rglru_scan(z: torch.Tensor, rb: torch.Tensor, ib: torch.Tensor, decay: torch.Tensor, u: torch.Tensor,
                y: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, seq_ctx: torch.Tensor,
                seq_slot: torch.Tensor, n_seqs: int) -> torch.Tensor:

@@ -93,6 +93,9 @@ _SIGNATURES = {
     "tk_seq_conv": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, P, L, P, L, I, I, I, I, I, P, P, I, I, I, I, I, I, P],
     "tk_attn_pointwise_rows": [],
     "tk_attn_pointwise": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, F, I, P, P, P, I, P],
+    "tk_attn_pointwise_mma_supported": [I, I, I, I, I],
+    "tk_attn_pointwise_mma_tokens": [I, I],
+    "tk_attn_pointwise_mma": [P, P, P, P, P, P, I, P, P, I, P, I, I, P, I, I, I, I, I, F, F, F, I, P, P, P, P],
     "tk_rglru_scan": [P, I, P, P, P, P, L, P, L, P, P, P, P, I, P, I, I, I, P],
     "tk_mlstm_scan": [P, L, I, I, I, P, L, F, F, P, P, P, P, P, I, P, P, I, I, I, I, P],
     "tk_mlstm_norm_gate": [P, P, P, P, P, L, P, P, P, P, I, I, I, F, I, P],
@@ -146,7 +149,8 @@ _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled"
             "tk_attn_mma_supported", "tk_attn_decode_fused_supported", "tk_attn_decode_fused_max_splits", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
             "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status",
             "tk_attn_latent_rows", "tk_attn_latent_max_rank", "tk_gemm_grouped_tile", "tk_attn_latent_mma_rows",
-            "tk_attn_latent_mma_supported", "tk_attn_pointwise_rows"}
+            "tk_attn_latent_mma_supported", "tk_attn_pointwise_rows", "tk_attn_pointwise_mma_supported",
+            "tk_attn_pointwise_mma_tokens"}
 
 
 _fns: dict = {}

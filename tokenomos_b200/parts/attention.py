@@ -241,9 +241,37 @@ class Attention:
             ops.sigmoid_gate(out, gate)
         return out
 
+    # whether pointwise weights may take the tensor-core kernels (TOKENOMOS_B200_ATTN_POINT_MMA=0: never)
+    pointwise_mma = os.environ.get("TOKENOMOS_B200_ATTN_POINT_MMA", "1") != "0"
+
     def _attend_pointwise(self, q, pool, table, ctx: StepContext) -> torch.Tensor:
-        """Weights of their own per key (no softmax): the CUDA-core kernel."""
+        """Weights of their own per key (no softmax): the tensor-core kernels where they take the
+        shape (bfloat16, keys and values of one size, 64 or 128), prompt portions in tiles of 64 rows
+        and single tokens shared out over their keys; else the CUDA-core kernel (any sizes, 32-bit
+        storage, weights that stay 32-bit with ``exact``)."""
         w = self.pointwise
+        if (self.pointwise_mma and not self.exact and ops.attention_pointwise_mma_supported(
+                self.heads, self.kv_heads, self.head_dim, self.v_dim, pool.shape[-1], q.dtype)):
+            out = torch.empty_like(q)
+            per_tile = ops.attention_pointwise_mma_tokens(self.heads, self.kv_heads)
+            decode_only = ctx.host.decode_only
+            tok0 = ntok = singles = None
+            n_single, nsplit = 0, 1
+            if not decode_only:
+                _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
+                singles = ctx.singles()
+                n_single = singles.numel()
+            else:
+                n_single = ctx.n_tokens
+            if n_single:
+                longest = ctx.host.longest
+                if self.window is not None:
+                    longest = min(longest, self.window)
+                nsplit = self.decode_splits(n_single, self.kv_heads, longest, self.tuning)
+            ops.attention_pointwise_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, singles, n_single,
+                                        nsplit, self.window, self.scale, w.cap, w.temp_coef, w.temp_every, w.r1, w.r2,
+                                        w.head_bias)
+            return out
         rows = ops.attention_pointwise_rows()
         group = self.heads // self.kv_heads
         per_tile = max(1, rows // group)
