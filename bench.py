@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import statistics
 import subprocess
 import sys
@@ -1250,6 +1251,268 @@ def laposun_kernels(z: dict, pk: dict) -> list[dict]:
     return rows
 
 
+# ---------------------------------------------------------------------------------------------
+# --design lisorax: the Lisorax decoder beside Laposun (the other design with an input
+# convolution, a 32-bit stream and experts) at equal sizes
+# ---------------------------------------------------------------------------------------------
+LISORAX_SIZES = {
+    # the Laposun side reads its own keys; Lisorax reads width, heads, kv_heads, dim, experts, top,
+    # expert_ff, taps, layers, vocab and the recurrent mixers' sizes
+    "w2048": dict(LAPOSUN_SIZES["w2048"], rec_width=2048, rec_blocks=16, mem_heads=8, mem_dim=128, mem_vdim=256),
+    "w1024": dict(LAPOSUN_SIZES["w1024"], rec_width=1024, rec_blocks=8, mem_heads=4, mem_dim=64, mem_vdim=256),
+}
+
+
+def lisorax_config(z: dict) -> dict:
+    """Groups of four layers: matrix memory, attention, gated recurrence, attention that reads the
+    first one's keys and values; every layer has experts."""
+    layers = []
+    mlp = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 0:
+            layer = {"type": "mlstm", "mixer": {"heads": z["mem_heads"], "dim": z["mem_dim"], "vdim": z["mem_vdim"],
+                                                "gate_cap": 15.0}}
+        elif kind == 2:
+            layer = {"type": "rglru", "mixer": {"width": z["rec_width"], "blocks": z["rec_blocks"], "conv": z["taps"]}}
+        else:
+            mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                     "scale": z["dim"] ** -0.5, "conv": z["taps"], "softcap": 30.0, "q_temp": {"coef": 0.2, "every": 512}}
+            if kind == 3:
+                mixer["kv_from"] = i - 2
+            layer = {"type": "attention", "mixer": mixer}
+        layers.append(dict(layer, mlp=mlp))
+    return {"architecture": "Lisorax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "canon": {"taps": z["taps"]}, "embedding": {"scale": 1.0}, "layers": layers}
+
+
+def lisorax_prefill_flops(z: dict, tokens: int) -> float:
+    """Multiply-adds times two of one prompt of ``tokens`` tokens as the design defines it (the matrix
+    memory as its recurrence: an update and a read of [dim, vdim + 1] per token and head)."""
+    W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    R, B = z["rec_width"], z["rec_blocks"]
+    Hm, Dm, Vm = z["mem_heads"], z["mem_dim"], z["mem_vdim"]
+    ff = 3 * W * z["top"] * z["expert_ff"] + W * z["experts"]
+    pairs = tokens * (tokens + 1) / 2
+    flops = 0.0
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 0:
+            per_tok = W * (2 * Hm * Dm + 2 * Hm * Vm + 2 * Hm) + Hm * Vm * W + 2 * Hm * Dm * (Vm + 1)
+        elif kind == 2:
+            per_tok = 2 * W * R + 2 * R * (R // B) + R * W
+        else:
+            per_tok = W * D * (H + (2 * G if kind == 1 else 0)) + H * D * W
+            flops += 2.0 * 2 * H * D * pairs
+        flops += 2.0 * tokens * (per_tok + ff)
+    return flops + 2.0 * z["vocab"] * W
+
+
+def lisorax_kernels(z: dict, pk: dict) -> list[dict]:
+    """Each kernel of the Lisorax path beside the kernel of an earlier model that does the like work, on
+    the shapes of a 2,048-token prompt portion of one sequence (or 64 decoded tokens behind 2,048
+    positions), L2 flushed before every launch, CUDA events around the launches, median of 20.
+    ``frac``: bytes over time against the measured copy bandwidth, or flops over time against the
+    measured bf16 rate."""
+    import torch
+
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.rope import Rotary
+
+    bf, dev = torch.bfloat16, "cuda"
+    T, W, H, G, D, P = 2048, z["width"], z["heads"], z["kv_heads"], z["dim"], 16
+    S, taps = z["streams"], z["taps"]
+    R, B = z["rec_width"], z["rec_blocks"]
+    Hm, Dm, Vm = z["mem_heads"], z["mem_dim"], z["mem_vdim"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def add(name, ours_us, theirs_us, ours_work, theirs_work, unit, like):
+        peak = pk["hbm_gbs"] * 1e3 if unit == "bytes" else pk["bf16_tflops"] * 1e6       # per microsecond
+        fo = ours_work / ours_us / peak
+        row = {"kernel": name, "like": like, "unit": unit, "lisorax_us": round(ours_us, 1), "lisorax_frac": round(fo, 4)}
+        if theirs_us is not None:
+            ft = theirs_work / theirs_us / peak
+            row.update(like_us=round(theirs_us, 1), like_frac=round(ft, 4), times_further_from_roofline=round(ft / fo, 2))
+        rows.append(row)
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    cu, zero1, one1 = i32([0, T]), i32([0]), i32([1])
+    tile = 16
+    n_t = T // tile
+    tiles = (torch.zeros(n_t, dtype=torch.int32, device=dev), torch.arange(0, T, tile, dtype=torch.int32, device=dev),
+             torch.arange(0, T, tile, dtype=torch.int32, device=dev), torch.full((n_t,), tile, dtype=torch.int32, device=dev))
+    nw = torch.ones(W, device=dev)
+
+    # 1. the stream: add of both sublayers' outputs + norm (16-bit and unrounded) + input convolution
+    res32 = torch.randn(T, W, device=dev)
+    y = torch.randn(T, W, device=dev).to(bf)
+    y2 = torch.randn(T, W, device=dev).to(bf)
+    tp = torch.randn(W, taps, device=dev) * 0.1
+    state = torch.zeros(2, taps - 1, W, device=dev)
+
+    def read():
+        h, h32, st = ops.stream32_add_norm(res32, y, nw, 1e-6, rows_add=y2, wide=True)
+        return ops.seq_conv(h32, tp, None, state, cu, zero1, one1, tiles, bf, residual=True)
+
+    streams = torch.randn(T, S * W, device=dev)
+    mix, ow, iw = torch.eye(S, device=dev).reshape(-1).contiguous(), torch.ones(S, device=dev), torch.ones(S, device=dev)
+
+    def read_like():
+        h = ops.hc_mix_norm(streams, y, mix, ow, iw, nw, 1e-6, S, bf, True)
+        return ops.canon_conv(h, tp, state, cu, zero1, one1, tiles, bf)
+
+    add("residual add of two sublayers + norm + input convolution (2 kernels)", _timed_us(read, flush),
+        _timed_us(read_like, flush), T * W * (4 + 2 + 2 + 4 + 2 + 4 + 4 + 2), T * W * (8 * S + 2 + 2), "bytes",
+        "Laposun: connections + norm + input convolution (2 kernels)")
+
+    # 2. q/k/v convolution with the cache write
+    pages = T // P + 1
+    pool = torch.zeros(pages, 2, G, P, D, dtype=bf, device=dev)
+    tbl = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1)
+    qkv = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+    ctaps = torch.randn((H + 2 * G) * D, taps, device=dev) * 0.3
+    cstate = torch.zeros(2, taps - 1, (H + 2 * G) * D, device=dev)
+    rot = Rotary(D, D, 1e6, "half", None, dev)
+    add("q/k/v convolution + cache write",
+        _timed_us(lambda: ops.seq_conv(qkv, ctaps, None, cstate, cu, zero1, one1, tiles, bf, out_channels=H * D,
+                                       kv=(pool, tbl, P, G, D, D)), flush),
+        _timed_us(lambda: ops.rotary_write(qkv, pool, rot.freq, 1.0, pos, seq, tbl, H, G, D, D, P, False, False), flush),
+        T * (H + 2 * G) * D * 4, T * (H + 2 * G) * D * 4, "bytes", "Darizen: rotation + cache write")
+
+    # 3. prompt attention (no window: every earlier key)
+    q = ops.seq_conv(qkv, ctaps, None, cstate, cu, zero1, one1, tiles, bf, out_channels=H * D,
+                     kv=(pool, tbl, P, G, D, D)).view(T, H, D)
+    out = torch.empty_like(q)
+    r1, r2, hb = torch.rand(H, device=dev), torch.rand(H, device=dev) * 0.3, torch.full((H,), -3.0, device=dev)
+    pairs = T * (T + 1) / 2
+    per = ops.attention_pointwise_mma_tokens(H, G)
+    t0 = torch.arange(0, T, per, dtype=torch.int32, device=dev)
+    nt = torch.full_like(t0, per)
+    ours = _timed_us(lambda: ops.attention_pointwise_mma(q, pool, out, pos, seq, tbl, t0, nt, None, 0, 1, None, D ** -0.5,
+                                                         30.0, 0.2, 512, r1, r2, hb), flush, reps=5)
+    per_d = ops.attention_prefill_mma_tokens(H, G)
+    t0d = torch.arange(0, T, per_d, dtype=torch.int32, device=dev)
+    add("prompt attention, pointwise weights (mma.sync)", ours,
+        _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, tbl, t0d, torch.full_like(t0d, per_d), None,
+                                                    D ** -0.5), flush, reps=5),
+        4.0 * pairs * H * D, 4.0 * pairs * H * D, "flops", "Darizen: prompt attention, softmax (mma.sync)")
+    if ops.attention_prefill_tc_supported(H, G, D, bf):
+        per_c = ops.attention_prefill_tc_tokens(H, G)
+        t0c = torch.arange(0, T, per_c, dtype=torch.int32, device=dev)
+        add("prompt attention, pointwise weights (mma.sync)", ours,
+            _timed_us(lambda: ops.attention_prefill_tc(q, pool, out, pos, seq, tbl, t0c, torch.full_like(t0c, per_c), None,
+                                                       D ** -0.5, None, 1), flush, reps=5),
+            4.0 * pairs * H * D, 4.0 * pairs * H * D, "flops", "Darizen: prompt attention, softmax (tcgen05)")
+
+    # 4. decode attention: 64 sequences behind T positions (sharing the pages; the bytes are read per sequence)
+    Bd = 64
+    dpos = torch.full((Bd,), T - 1, dtype=torch.int32, device=dev)
+    dseq = torch.arange(Bd, dtype=torch.int32, device=dev)
+    dtbl = tbl.expand(Bd, -1).contiguous()
+    dq, dout = q[:Bd].contiguous(), torch.empty_like(q[:Bd])
+    add("decode attention, pointwise weights, 64 tokens",
+        _timed_us(lambda: ops.attention_pointwise_mma(dq, pool, dout, dpos, dseq, dtbl, None, None, None, Bd, 2, None,
+                                                      D ** -0.5, 30.0, 0.2, 512, r1, r2, hb), flush),
+        _timed_us(lambda: ops.attention_decode_mma(dq, pool, dout, dpos, dseq, dtbl, None, None, D ** -0.5, 2), flush),
+        Bd * G * T * D * 2 * 2, Bd * G * T * D * 2 * 2, "bytes", "Darizen: decode attention, softmax")
+
+    # 5. gated linear recurrence: the scan (gates' products in, gated output out) beside LFM3's gated short conv
+    u = torch.randn(T, 2 * R, device=dev).to(bf)
+    zg = torch.randn(B, T, 2 * (R // B), device=dev)
+    rb, ib, dec = torch.zeros(R, device=dev), torch.zeros(R, device=dev), -torch.rand(R, device=dev)
+    sst = torch.zeros(2, R, device=dev)
+    bcx = torch.randn(T, 3 * R, device=dev).to(bf)
+    cw = torch.randn(R, 3, device=dev)
+    cst = torch.zeros(2, 2, R, dtype=bf, device=dev)
+    add("gated linear recurrence: scan over 2,048 tokens of one sequence",
+        _timed_us(lambda: ops.rglru_scan(zg, rb, ib, dec, u[:, R:], u[:, :R], sst, cu, zero1, one1, 1), flush),
+        _timed_us(lambda: ops.conv_gated(bcx, cw, None, cst, cu, zero1, one1, tiles[0], tiles[2], tiles[3], tile_cap=tile,
+                                         tile_tok0=tiles[1]), flush),
+        T * R * (8 + 2 + 2 + 2), T * R * (6 + 2), "bytes", "LFM3: gated short convolution")
+    cu64 = torch.arange(0, T + 1, T // 64, dtype=torch.int32, device=dev)
+    z64, o64 = torch.zeros(64, dtype=torch.int32, device=dev), torch.arange(1, 65, dtype=torch.int32, device=dev)
+    sst64 = torch.zeros(66, R, device=dev)
+    add("gated linear recurrence: scan over 2,048 tokens of 64 sequences",
+        _timed_us(lambda: ops.rglru_scan(zg, rb, ib, dec, u[:, R:], u[:, :R], sst64, cu64, z64, o64, 64), flush), None,
+        T * R * (8 + 2 + 2 + 2), 0, "bytes", "none")
+    add("gated linear recurrence: one token of 64 sequences",
+        _timed_us(lambda: ops.rglru_scan(zg[:, :64].contiguous(), rb, ib, dec, u[:64, R:], u[:64, :R], sst64,
+                                         torch.arange(0, 65, dtype=torch.int32, device=dev), o64, o64, 64), flush), None,
+        64 * R * (8 + 2 + 2 + 2 + 8), 0, "bytes", "none")
+
+    # 6. matrix memory: the scan and its norm + gate
+    mq = torch.randn(T, 2 * Hm * Dm + 2 * Hm * Vm, device=dev).to(bf) * 0.3
+    mg = torch.randn(T, 2 * Hm + (-2 * Hm % 8), device=dev)
+    mS = torch.zeros(66, Hm, Vm + 1, Dm, device=dev)
+    mm = torch.zeros(66, Hm, device=dev)
+    mw = torch.ones(Hm * Vm, device=dev)
+    g0 = 2 * Hm * Dm + Hm * Vm
+
+    mem_flops = 2.0 * T * Hm * Dm * (Vm + 1) * 2
+    add("matrix memory: scan over 2,048 tokens of one sequence (32-bit, CUDA cores)",
+        _timed_us(lambda: ops.mlstm_scan(mq, (0, Hm * Dm, 2 * Hm * Dm), mg, 15.0, Dm ** -0.5, mS, mm, cu, zero1, one1, 1, Hm,
+                                         Dm, Vm), flush, reps=5),
+        None, mem_flops, 0, "flops", "none (of the bf16 tensor rate; the state's arithmetic is 32-bit)")
+    add("matrix memory: scan over 2,048 tokens of 64 sequences (32-bit, CUDA cores)",
+        _timed_us(lambda: ops.mlstm_scan(mq, (0, Hm * Dm, 2 * Hm * Dm), mg, 15.0, Dm ** -0.5, mS, mm, cu64, z64, o64, 64, Hm,
+                                         Dm, Vm), flush, reps=5),
+        None, mem_flops, 0, "flops", "none (of the bf16 tensor rate; the state's arithmetic is 32-bit)")
+    cu1 = torch.arange(0, 65, dtype=torch.int32, device=dev)
+    add("matrix memory: one token of 64 sequences (state read and written)",
+        _timed_us(lambda: ops.mlstm_scan(mq[:64], (0, Hm * Dm, 2 * Hm * Dm), mg[:64], 15.0, Dm ** -0.5, mS, mm, cu1, o64, o64,
+                                         64, Hm, Dm, Vm), flush),
+        _timed_us(lambda: ops.attention_decode_mma(dq, pool, dout, dpos, dseq, dtbl, None, None, D ** -0.5, 2), flush),
+        64 * Hm * (Vm + 1) * Dm * 8, Bd * G * T * D * 2 * 2, "bytes", "Darizen: decode attention, softmax")
+    num, m = ops.mlstm_scan(mq, (0, Hm * Dm, 2 * Hm * Dm), mg, 15.0, Dm ** -0.5, mS, mm, cu, zero1, one1, 1, Hm, Dm, Vm)
+    add("matrix memory: division + head norm + gate",
+        _timed_us(lambda: ops.mlstm_norm_gate(num, m, mm, mw, mq[:, g0:g0 + Hm * Vm], seq, cu, one1, 1e-6, bf), flush),
+        _timed_us(lambda: ops.stream32_add_norm(res32, y, nw, 1e-6), flush),
+        T * Hm * (Vm * (4 + 2 + 2) + 8), T * W * (4 + 2 + 4 + 2), "bytes", "Darizen: residual add + norm")
+
+    # 7. the experts (gate | up in one grouped product, the activation, down) beside Laposun's (up with
+    # the activation in its epilogue, down)
+    E, top, ff = z["experts"], z["top"], z["expert_ff"]
+    x = torch.randn(T, W, device=dev).to(bf)
+    up2 = torch.randn(E, 2 * ff, W, device=dev).to(bf) * 0.02
+    up1 = up2[:, :ff].contiguous()
+    down = torch.randn(E, W, ff, device=dev).to(bf) * 0.02
+    idx, wgt, gate = ops.moe_route(torch.randn(T, E, device=dev), E, top, 1.0, False)
+    if hasattr(torch, "_grouped_mm"):
+        r8, p8, _, ends = ops.moe_sort(idx, E, 8, ends=True)
+
+        def gated():
+            a = ops.swiglu(torch._grouped_mm(ops.gather_rows_or_zero(x, r8), up2.transpose(1, 2), offs=ends))
+            return torch._grouped_mm(a, down.transpose(1, 2), offs=ends)
+
+        def squared():
+            a = ops.relu2(torch._grouped_mm(ops.gather_rows_or_zero(x, r8), up1.transpose(1, 2), offs=ends))
+            return torch._grouped_mm(a, down.transpose(1, 2), offs=ends)
+
+        add("experts: gather + grouped gate|up + SwiGLU + grouped down (as a 2,048-token step runs)",
+            _timed_us(gated, flush, reps=5), _timed_us(squared, flush, reps=5), 6.0 * T * top * ff * W,
+            4.0 * T * top * ff * W, "flops", "Laposun: gather + grouped up + relu^2 + grouped down")
+    xs = x[:64].contiguous()
+    idx64 = idx[:64].contiguous()
+    tl = ops.gemm_grouped_tiles(bf, math.gcd(2 * ff, W), math.gcd(ff, W), 64 * top)
+    rt64, pr64, te64 = ops.moe_sort(idx64, E, tl)
+
+    def gated_small():
+        a = ops.swiglu(ops.gemm_grouped(xs, up2, te64, rt64, rt64.numel(), tile=tl))
+        return ops.gemm_grouped(a, down, te64, None, rt64.numel(), tile=tl)
+
+    def squared_small():
+        a = ops.gemm_grouped(xs, up1, te64, rt64, rt64.numel(), act=True, tile=tl)
+        return ops.gemm_grouped(a, down, te64, None, rt64.numel(), tile=tl)
+
+    touched = min(E, 64 * top)
+    add("experts: 64 decoded tokens, own grouped kernel (gate|up, SwiGLU kernel, down)", _timed_us(gated_small, flush),
+        _timed_us(squared_small, flush), touched * 3 * ff * W * 2, touched * 2 * ff * W * 2, "bytes",
+        "Laposun: up with relu^2 in the epilogue, down")
+    return rows
+
 def run_design(name: str, args, warmup: int) -> int:
     """``--design darizen``: decode (batch 8 and 64) and prefill (2,048 tokens) throughput of
     Darizen stacks at a few real layer sizes, beside the LFM3 stack of sliding-window attention
@@ -1262,19 +1525,26 @@ def run_design(name: str, args, warmup: int) -> int:
     from tokenomos_b200.weights import write_model_folder
 
     pk = peaks()
-    sizes = LAPOSUN_SIZES if name == "laposun" else DESIGN_SIZES
+    sizes = {"laposun": LAPOSUN_SIZES, "lisorax": LISORAX_SIZES}.get(name, DESIGN_SIZES)
     for size, z in sizes.items():
         if getattr(args, "design_size", None) and size != args.design_size:
             continue
         line = {"design": name, "size": size, "sizes": z, "dtype": "bf16",
                 "data": "synthetic token ids, random-init weights N(0, 0.02)"}
-        arms = ((("laposun", laposun_config(z)), ("darizen", darizen_config(z))) if name == "laposun" else
-                (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z))))
+        arms = {"laposun": (("laposun", laposun_config(z)), ("darizen", darizen_config(z))),
+                "lisorax": (("lisorax", lisorax_config(z)), ("laposun", laposun_config(z)))}.get(
+                    name, (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z))))
         for arm, config in arms:
             with tempfile.TemporaryDirectory(prefix="tokenomos_b200_design_") as tmp:
                 folder = Path(tmp) / arm
                 if arm != "lfm3":
                     write_model_folder(folder, config, 0, 0.02, 0.0, torch.bfloat16)
+                    if arm == "lisorax":
+                        # the distance bias takes the logarithm of 1 + r2 * distance: its numbers are not negative
+                        from safetensors.torch import load_file, save_file
+                        tensors = load_file(str(folder / "model.safetensors"))
+                        save_file({k: (v.abs() if k.endswith((".r1", ".r2")) else v) for k, v in tensors.items()},
+                                  str(folder / "model.safetensors"))
                 else:
                     write_folder(folder, z["layers"], config)
                 model = models.load(str(folder), "cuda", models.configure(str(folder), work="bf16"))
@@ -1285,13 +1555,14 @@ def run_design(name: str, args, warmup: int) -> int:
                 res[f"decode_b{batch}"] = {"tok_s": round(d["tok_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
                                            "launches": d["launches_per_step"]}
             pf = device_prefill(model, cfg, args.page)
-            flops = laposun_prefill_flops(z, pf["tokens"]) if arm == "laposun" else pf["flops"]
+            flops = {"laposun": laposun_prefill_flops, "lisorax": lisorax_prefill_flops}.get(
+                arm, lambda *_: pf["flops"])(z, pf["tokens"])
             res["prefill_2048"] = {"tok_s": round(pf["tok_s"], 1), "ms": round(pf["ms"], 3),
                                    "frac": round(flops / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
             line[arm] = res
             del model
             torch.cuda.empty_cache()
-        line["kernels"] = laposun_kernels(z, pk) if name == "laposun" else design_kernels(z, pk)
+        line["kernels"] = {"laposun": laposun_kernels, "lisorax": lisorax_kernels}.get(name, design_kernels)(z, pk)
         print(json.dumps(line), flush=True)
     return 0
 
@@ -1320,9 +1591,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--trace", default=None,
                     help="--workload: write one JSON record per step of an extra pass to this file")
-    ap.add_argument("--design", default=None, choices=["darizen", "laposun"],
+    ap.add_argument("--design", default=None, choices=["darizen", "laposun", "lisorax"],
                     help="the named design beside the closest existing model at equal sizes instead (darizen beside "
-                         "LFM3, laposun beside darizen)")
+                         "LFM3, laposun beside darizen, lisorax beside laposun)")
     ap.add_argument("--design-size", default=None, help="only this size of the design's table")
     ap.add_argument("--sweep", action="store_true",
                     help="decode and prefill at other batch sizes and context lengths instead")
