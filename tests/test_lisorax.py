@@ -657,6 +657,29 @@ def test_gated_recurrence_keeps_a_slow_channel_over_hundreds_of_tokens(tmp_path)
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mixer_of", ["rglru", "mlstm"])
+def test_recurrent_mixers_on_long_portions(mixer_of, dtype, tmp_path):
+    """Portions of hundreds of tokens take the kernels that cut the time axis (slices side by side
+    for the gated recurrence, staged rounds for the matrix memory): a portion from a zero state, one
+    that goes on from a stored state, a single token of another request beside a long portion, and
+    lengths that leave slices and rounds partly or wholly empty."""
+    width = 40
+    if mixer_of == "rglru":
+        layer, ref = rglru(width=72, blocks=3, conv=4), plain.rglru_mixer
+    else:
+        layer, ref = mlstm(heads=2, dim=40, vdim=9, cap=8.0), lambda *a: plain.mlstm_mixer(*a, 1e-5)
+    rig = Rig([dict(layer, mlp=None)], width, dtype, tmp_path, seed=12, pages=400)
+    lengths = {"a": 903, "b": 3, "c": 531}
+    x = rows_for(lengths, width, 9)
+    plans = {"a": [(0, 300), (300, 301), (301, 903)], "b": [(0, 1), (1, 2), (2, 3)], "c": [(0, 530), (530, 531)]}
+    mixer = rig.model.blocks[0].mixer
+    got = rig.run(x, plans, lambda rows, ctx: mixer.forward(rows, ctx, 0))
+    want = {rid: ref(rig.w, "l0.mix.", rig.config["layers"][0]["mixer"], x[rid]) for rid in lengths}
+    close(got, want, 3e-5 if dtype == "float32" else 5e-2, f"{mixer_of} long portions {dtype}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("how", ["whole", "decoded", "portions", "tokens"])
 @pytest.mark.parametrize("case", [dict(heads=3, dim=16, vdim=24, cap=6.0), dict(heads=1, dim=24, vdim=8, cap=15.0),
                                   dict(heads=2, dim=10, vdim=6, cap=3.0), dict(heads=2, dim=64, vdim=128, cap=10.0),

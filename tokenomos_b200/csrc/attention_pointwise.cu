@@ -212,25 +212,41 @@ TK_API int tk_attn_pointwise(const void* q, const void* kv_pool, void* out, cons
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-struct RowConst { float scale, a1, a2, hb; };
+// A row's constants, with the weight carried in base-2 logarithms so that every special function is
+// one instruction: with E = 2^(c1 dot), the negated score times log2(e) is
+//     s2 = k2 / (1 + E) + k0 + a1 log2(1 + a2 dist),   k2 = 2 cap log2(e), k0 = -(cap + hb) log2(e)
+// (cap tanh(z) = cap - 2 cap / (1 + e^(2z)), c1 = 2 scale log2(e) / cap), and the weight 1 / (1 + 2^s2).
+// Without a cap s2 = c1 dot + k0 + ..., c1 = -scale log2(e), k0 = -hb log2(e).
+struct RowConst { float c1, k2, k0, a1, a2; };
 
-__device__ __forceinline__ float point_weight_fast(float dot, const RowConst& rc, float cap, float inv_cap, bool has_r,
-                                                   int dist) {
-    float s = dot * rc.scale;
-    if (cap > 0.f) {
-        const float z = fminf(fmaxf(s * inv_cap, -15.f), 15.f);
-        s = cap * (1.f - __fdividef(2.f, 1.f + __expf(2.f * z)));
-    }
-    if (has_r) s -= rc.a1 * __logf(fmaf(rc.a2, (float)dist, 1.f));
-    s = fmaxf(s + rc.hb, -80.f);
-    return __fdividef(1.f, 1.f + __expf(-s));
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lg2_fast(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// an overflowing power of two is +inf and its reciprocal 0: the limits come out without clamps
+__device__ __forceinline__ float point_weight_fast(float dot, const RowConst& rc, bool capped, bool has_r, float dist) {
+    float s2 = capped ? fmaf(rc.k2, rcp_fast(1.f + ex2_fast(dot * rc.c1)), rc.k0) : fmaf(dot, rc.c1, rc.k0);
+    if (has_r) s2 = fmaf(rc.a1, lg2_fast(fmaf(rc.a2, dist, 1.f)), s2);
+    return rcp_fast(1.f + ex2_fast(s2));
 }
 
 // keys k0 .. k0 + NK - 1 of a staged 64-key tile whose first key is position j0
 template <int D, int NK>
 __device__ __forceinline__ void point_block(const uint32_t (&qf)[D / 16][4], uint32_t ktile, uint32_t vtile, int k0,
                                             int j0, int pos_lo, int pos_hi, const RowConst& rlo, const RowConst& rhi,
-                                            float cap, float inv_cap, bool has_r, int window, float (&o)[D / 8][4]) {
+                                            bool capped, bool has_r, int window, float (&o)[D / 8][4]) {
     const int lane = threadIdx.x & 31;
     const int t = lane & 3;
     const int mi = lane >> 3, r = lane & 7;
@@ -251,15 +267,17 @@ __device__ __forceinline__ void point_block(const uint32_t (&qf)[D / 16][4], uin
         }
     }
     uint32_t pf[NK / 16][4];
+    const float pos_lo_f = (float)pos_lo, pos_hi_f = (float)pos_hi, key_f = (float)(j0 + k0 + 2 * t);
+    const float window_f = window > 0 ? (float)window : INFINITY;
 #pragma unroll
     for (int n = 0; n < NK / 8; ++n) {
         float p[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int j = j0 + k0 + n * 8 + 2 * t + (e & 1);
-            const int dist = ((e < 2) ? pos_lo : pos_hi) - j;          // a padding row's position is -1
-            const bool visible = dist >= 0 && (window <= 0 || dist < window);
-            p[e] = visible ? point_weight_fast(s[n][e], (e < 2) ? rlo : rhi, cap, inv_cap, has_r, dist) : 0.f;
+            // distances as differences of floats (exact below 2^24): no conversion per score
+            const float dist = ((e < 2) ? pos_lo_f : pos_hi_f) - (key_f + (float)(n * 8 + (e & 1)));
+            const bool visible = dist >= 0.f && dist < window_f;         // a padding row's position is -1
+            p[e] = visible ? point_weight_fast(s[n][e], (e < 2) ? rlo : rhi, capped, has_r, dist) : 0.f;
         }
         // the C layout of two neighbouring 8-key tiles is the A layout of one 16-key step
         pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
@@ -345,18 +363,27 @@ attn_pointwise_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __n
     const int pos_lo = r_lo < rows ? pos_first + r_lo / G : -1;
     const int pos_hi = r_hi < rows ? pos_first + r_hi / G : -1;
     const bool has_r = opt.r1 != nullptr;
+    const bool capped = opt.cap > 0.f;
     auto row_const = [&](int r, int pos) {
-        RowConst c{0.f, 0.f, 0.f, 0.f};
+        RowConst c{0.f, 0.f, 0.f, 0.f, 0.f};
         if (pos >= 0) {
+            constexpr float LOG2E = 1.4426950408889634f;
             const int head = kvh * G + r % G;
-            c.scale = opt.scale * temperature(opt, pos);
+            const float scale = opt.scale * temperature(opt, pos);
+            const float hb = opt.head_bias != nullptr ? opt.head_bias[head] : 0.f;
             if (has_r) c.a1 = opt.r1[head], c.a2 = opt.r2[head];
-            if (opt.head_bias != nullptr) c.hb = opt.head_bias[head];
+            if (capped) {
+                c.c1 = 2.f * LOG2E * scale / opt.cap;
+                c.k2 = 2.f * LOG2E * opt.cap;
+                c.k0 = -LOG2E * (opt.cap + hb);
+            } else {
+                c.c1 = -LOG2E * scale;
+                c.k0 = -LOG2E * hb;
+            }
         }
         return c;
     };
     const RowConst rlo = row_const(r_lo, pos_lo), rhi = row_const(r_hi, pos_hi);
-    const float inv_cap = opt.cap > 0.f ? 1.f / opt.cap : 0.f;
     // the warp's own key range: nothing above its last row's position, nothing a window hides
     const int w_last_row = min(rows, row0 + 16) - 1;
     const int w_pos_max = w_last_row >= row0 ? pos_first + w_last_row / G : -1;
@@ -400,10 +427,10 @@ attn_pointwise_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __n
         if (SINGLE) {
             const int k0 = warp * 16;
             if (w_pos_max >= j0 + k0 && (opt.window <= 0 || j0 + k0 + 15 > w_pos_min - opt.window))
-                point_block<D, 16>(qf, base, base + TILE_BYTES, k0, j0, pos_lo, pos_hi, rlo, rhi, opt.cap, inv_cap,
+                point_block<D, 16>(qf, base, base + TILE_BYTES, k0, j0, pos_lo, pos_hi, rlo, rhi, capped,
                                    has_r, opt.window, o);
         } else if (w_pos_max >= j0 && (opt.window <= 0 || j0 + 63 > w_pos_min - opt.window)) {
-            point_block<D, 64>(qf, base, base + TILE_BYTES, 0, j0, pos_lo, pos_hi, rlo, rhi, opt.cap, inv_cap, has_r,
+            point_block<D, 64>(qf, base, base + TILE_BYTES, 0, j0, pos_lo, pos_hi, rlo, rhi, capped, has_r,
                                opt.window, o);
         }
     }

@@ -78,25 +78,34 @@ seq_conv_kernel(const TI* in, int64_t in_stride, const float* __restrict__ taps,
         page_part = ((size_t)which * dest.Hkv + e / D) * dest.P * dest.Dp + e % D;
     }
     const size_t page_size = (size_t)2 * dest.Hkv * dest.P * dest.Dp;
-    for (int i = 0; i < n; ++i) {
-        const float cur = to_f<TI>(in[(size_t)(tok0 + i) * in_stride + c]);
-        float acc = (residual ? cur : 0.f) + b;
-        acc = fmaf(w[K - 1], cur, acc);
+    constexpr int AHEAD = 8;                           // inputs in flight: the walk is bound by their latency
+    for (int i0 = 0; i0 < n; i0 += AHEAD) {
+        float ahead[AHEAD];
 #pragma unroll
-        for (int d = 1; d < MAX_TAPS; ++d)
-            if (d < K) acc = fmaf(w[K - 1 - d], past[d - 1], acc);
-        if (paged) {
-            const int pos = pos0 + i;
-            const int page = TK_PAGE(TK_K_SEQ_CONV, dest.block_table[(size_t)s * dest.bt_stride + pos / dest.P]);
-            reinterpret_cast<TO*>(dest.pool)[(size_t)page * page_size + page_part + (size_t)(pos % dest.P) * dest.Dp] =
-                from_f<TO>(acc);
-        } else {
-            out[(size_t)(tok0 + i) * out_stride + c] = from_f<TO>(acc);
-            if (plain != nullptr) plain[(size_t)(tok0 + i) * plain_stride + c] = from_f<TO>(cur);
+        for (int k = 0; k < AHEAD; ++k) ahead[k] = to_f<TI>(in[(size_t)(tok0 + min(i0 + k, n - 1)) * in_stride + c]);
+#pragma unroll
+        for (int k = 0; k < AHEAD; ++k) {
+            const int i = i0 + k;
+            if (i >= n) break;
+            const float cur = ahead[k];
+            float acc = (residual ? cur : 0.f) + b;
+            acc = fmaf(w[K - 1], cur, acc);
+#pragma unroll
+            for (int d = 1; d < MAX_TAPS; ++d)
+                if (d < K) acc = fmaf(w[K - 1 - d], past[d - 1], acc);
+            if (paged) {
+                const int pos = pos0 + i;
+                const int page = TK_PAGE(TK_K_SEQ_CONV, dest.block_table[(size_t)s * dest.bt_stride + pos / dest.P]);
+                reinterpret_cast<TO*>(dest.pool)[(size_t)page * page_size + page_part + (size_t)(pos % dest.P) * dest.Dp] =
+                    from_f<TO>(acc);
+            } else {
+                out[(size_t)(tok0 + i) * out_stride + c] = from_f<TO>(acc);
+                if (plain != nullptr) plain[(size_t)(tok0 + i) * plain_stride + c] = from_f<TO>(cur);
+            }
+#pragma unroll
+            for (int d = MAX_TAPS - 1; d >= 2; --d) past[d - 1] = past[d - 2];
+            past[0] = cur;
         }
-#pragma unroll
-        for (int d = MAX_TAPS - 1; d >= 2; --d) past[d - 1] = past[d - 2];
-        past[0] = cur;
     }
     if (off == 0 && st != nullptr) {
         const int first = cu_seqlens[s], len = cu_seqlens[s + 1] - first;

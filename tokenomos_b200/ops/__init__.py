@@ -1325,7 +1325,7 @@ def mlstm_scan(qkv: torch.Tensor, offsets: tuple, gates: torch.Tensor, cap: floa
     _lib.call("tk_mlstm_scan", _ptr(qkv), qkv.stride(0), int(offsets[0]), int(offsets[1]), int(offsets[2]), _ptr(gates),
               gates.stride(0), float(cap or 0.0), float(q_scale), _ptr(S_state), _ptr(m_state),
               _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")),
-              int(n_seqs), _ptr(num), _ptr(m), heads, dim, v_dim, _dtype_code(qkv), _stream())
+              int(n_seqs), T, _ptr(num), _ptr(m), heads, dim, v_dim, _dtype_code(qkv), _stream())
     return num, m
 
 

@@ -97,7 +97,7 @@ _SIGNATURES = {
     "tk_attn_pointwise_mma_tokens": [I, I],
     "tk_attn_pointwise_mma": [P, P, P, P, P, P, I, P, P, I, P, I, I, P, I, I, I, I, I, F, F, F, I, P, P, P, P],
     "tk_rglru_scan": [P, I, P, P, P, P, L, P, L, P, P, P, P, I, P, I, I, I, P],
-    "tk_mlstm_scan": [P, L, I, I, I, P, L, F, F, P, P, P, P, P, I, P, P, I, I, I, I, P],
+    "tk_mlstm_scan": [P, L, I, I, I, P, L, F, F, P, P, P, P, P, I, I, P, P, I, I, I, I, P],
     "tk_mlstm_norm_gate": [P, P, P, P, P, L, P, P, P, P, I, I, I, F, I, P],
 }
 
