@@ -1341,9 +1341,15 @@ def lisorax_kernels(z: dict, pk: dict) -> list[dict]:
     seq = torch.zeros(T, dtype=torch.int32, device=dev)
     cu, zero1, one1 = i32([0, T]), i32([0]), i32([1])
     tile = 16
-    n_t = T // tile
-    tiles = (torch.zeros(n_t, dtype=torch.int32, device=dev), torch.arange(0, T, tile, dtype=torch.int32, device=dev),
-             torch.arange(0, T, tile, dtype=torch.int32, device=dev), torch.full((n_t,), tile, dtype=torch.int32, device=dev))
+
+    def tiles_of(size):
+        k = T // size
+        return (torch.zeros(k, dtype=torch.int32, device=dev), torch.arange(0, T, size, dtype=torch.int32, device=dev),
+                torch.arange(0, T, size, dtype=torch.int32, device=dev), torch.full((k,), size, dtype=torch.int32, device=dev))
+
+    tiles = tiles_of(tile)
+    tiles_w = tiles_of(ops.seq_conv_tile(tile, T, W))                      # as the parts choose them for a step of T tokens
+    tiles_qkv = tiles_of(ops.seq_conv_tile(tile, T, (H + 2 * G) * D))
     nw = torch.ones(W, device=dev)
 
     # 1. the stream: add of both sublayers' outputs + norm (16-bit and unrounded) + input convolution
@@ -1355,7 +1361,7 @@ def lisorax_kernels(z: dict, pk: dict) -> list[dict]:
 
     def read():
         h, h32, st = ops.stream32_add_norm(res32, y, nw, 1e-6, rows_add=y2, wide=True)
-        return ops.seq_conv(h32, tp, None, state, cu, zero1, one1, tiles, bf, residual=True)
+        return ops.seq_conv(h32, tp, None, state, cu, zero1, one1, tiles_w, bf, residual=True)
 
     streams = torch.randn(T, S * W, device=dev)
     mix, ow, iw = torch.eye(S, device=dev).reshape(-1).contiguous(), torch.ones(S, device=dev), torch.ones(S, device=dev)
@@ -1377,7 +1383,7 @@ def lisorax_kernels(z: dict, pk: dict) -> list[dict]:
     cstate = torch.zeros(2, taps - 1, (H + 2 * G) * D, device=dev)
     rot = Rotary(D, D, 1e6, "half", None, dev)
     add("q/k/v convolution + cache write",
-        _timed_us(lambda: ops.seq_conv(qkv, ctaps, None, cstate, cu, zero1, one1, tiles, bf, out_channels=H * D,
+        _timed_us(lambda: ops.seq_conv(qkv, ctaps, None, cstate, cu, zero1, one1, tiles_qkv, bf, out_channels=H * D,
                                        kv=(pool, tbl, P, G, D, D)), flush),
         _timed_us(lambda: ops.rotary_write(qkv, pool, rot.freq, 1.0, pos, seq, tbl, H, G, D, D, P, False, False), flush),
         T * (H + 2 * G) * D * 4, T * (H + 2 * G) * D * 4, "bytes", "Darizen: rotation + cache write")

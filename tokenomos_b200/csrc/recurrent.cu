@@ -78,13 +78,15 @@ rglru_scan_kernel(const float* z, int Tz, const float* __restrict__ rb, const fl
 }
 
 // Long portions of few sequences: a sequence's portion is cut into RS_SL slices of equal length and a
-// block walks all of them at once, RS_CH channels wide. The recurrence is linear in S, so a slice is
+// block walks all of them at once, RS_CH channels wide (few channels a block: a portion of 2,048
+// tokens of 1,024 channels is 128 blocks). The recurrence is linear in S, so a slice is
 // the map S -> A S + B with A the product of its a_t and B what it leaves from zero: the first pass
 // forms (A, B) per slice, every thread then chains the slices before its own from the stored state,
 // and the second pass walks the slice again from there and writes the outputs.
 namespace {
-constexpr int RS_CH = 16;    // channels per block
-constexpr int RS_SL = 64;    // slices per portion
+constexpr int RS_CH = 8;     // channels per block
+constexpr int RS_SL = 128;   // slices per portion
+constexpr int RS_KEEP = 16;  // a slice of up to this many tokens keeps its (a_t, b_t) in registers between the passes
 }
 
 template <typename T>
@@ -114,26 +116,53 @@ rglru_scan_sliced_kernel(const float* __restrict__ z, int Tz, const float* __res
         a = expf(log_a);
         x = sqrtf(fmaxf(-expm1f(2.f * log_a), 0.f)) * i * to_f<T>(u[(size_t)t * u_stride + c]);
     };
-    float A = 1.f, B = 0.f;
-#pragma unroll 4
-    for (int t = t_begin; t < t_end; ++t) {
-        float a, x;
-        coef(t, a, x);
-        B = fmaf(a, B, x);
-        A *= a;
-    }
-    A_s[sl][cl] = A;
-    B_s[sl][cl] = B;
-    __syncthreads();
     float* st = state + (size_t)TK_SLOT(TK_K_RECURRENT, seq_slot[s]) * W + c;
     float S = seq_ctx[s] > 0 ? *st : 0.f;
-    for (int j = 0; j < sl; ++j) S = fmaf(A_s[j][cl], S, B_s[j][cl]);
+    float A = 1.f, B = 0.f;
+    if (per <= RS_KEEP) {
+        float ka[RS_KEEP], kx[RS_KEEP];
+        const int cnt = t_end - t_begin;
+#pragma unroll
+        for (int k = 0; k < RS_KEEP; ++k) {
+            ka[k] = 1.f;
+            kx[k] = 0.f;
+            if (k < cnt) coef(t_begin + k, ka[k], kx[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < RS_KEEP; ++k) {
+            B = fmaf(ka[k], B, kx[k]);
+            A *= ka[k];
+        }
+        A_s[sl][cl] = A;
+        B_s[sl][cl] = B;
+        __syncthreads();
+        for (int j = 0; j < sl; ++j) S = fmaf(A_s[j][cl], S, B_s[j][cl]);
+#pragma unroll
+        for (int k = 0; k < RS_KEEP; ++k) {
+            if (k >= cnt) break;
+            const int t = t_begin + k;
+            S = fmaf(ka[k], S, kx[k]);
+            if (live) out[(size_t)t * W + c] = from_f<T>(S * gelu_tanh(to_f<T>(y[(size_t)t * y_stride + c])));
+        }
+    } else {
 #pragma unroll 4
-    for (int t = t_begin; t < t_end; ++t) {
-        float a, x;
-        coef(t, a, x);
-        S = fmaf(a, S, x);
-        if (live) out[(size_t)t * W + c] = from_f<T>(S * gelu_tanh(to_f<T>(y[(size_t)t * y_stride + c])));
+        for (int t = t_begin; t < t_end; ++t) {
+            float a, x;
+            coef(t, a, x);
+            B = fmaf(a, B, x);
+            A *= a;
+        }
+        A_s[sl][cl] = A;
+        B_s[sl][cl] = B;
+        __syncthreads();
+        for (int j = 0; j < sl; ++j) S = fmaf(A_s[j][cl], S, B_s[j][cl]);
+#pragma unroll 4
+        for (int t = t_begin; t < t_end; ++t) {
+            float a, x;
+            coef(t, a, x);
+            S = fmaf(a, S, x);
+            if (live) out[(size_t)t * W + c] = from_f<T>(S * gelu_tanh(to_f<T>(y[(size_t)t * y_stride + c])));
+        }
     }
     if (live && sl == RS_SL - 1) *st = S;      // the slices after the portion's end are empty: this is the last state
 }
@@ -147,7 +176,7 @@ TK_API int tk_rglru_scan(const float* z, int Tz, const float* rb, const float* i
     TK_CHECK_ARG(W > 0 && blocks > 0 && W % blocks == 0, "gated recurrence: %d channels in %d blocks", W, blocks);
     TK_CHECK_ARG(n_seqs >= 0 && Tz >= 0, "gated recurrence: bad sizes");
     if (n_seqs == 0) return 0;
-    if (Tz >= 4 * RS_SL * n_seqs) {      // long portions: slices of the time axis side by side
+    if (Tz >= 2 * RS_SL * n_seqs) {      // long portions: slices of the time axis side by side
         dim3 sgrid((W + RS_CH - 1) / RS_CH, n_seqs);
         if (dtype == TK_F32)
             tk_launch(rglru_scan_sliced_kernel<float>, sgrid, dim3(RS_CH * RS_SL), 0, stream, z, Tz, rb, ib, decay,

@@ -1149,6 +1149,18 @@ def relu2(x: torch.Tensor) -> torch.Tensor:
 # ---- sequence convolutions, pointwise-weight attention, recurrent state updates ----------------------
 
 SEQ_CONV_MAX_TAPS = 8
+_SEQ_CONV_RESIDENT = 148 * 4      # blocks of the sequence convolution that run at once
+
+
+def seq_conv_tile(base: int, tokens: int, channels: int) -> int:
+    """The tile length for ``seq_conv`` on a step of ``tokens`` tokens: ``base``, doubled (up to 128)
+    while the tiles of all channel blocks would not run at once. A thread walks its tile in order,
+    so short tiles are quick, but a second wave of blocks costs more than a longer walk."""
+    tile = max(int(base), 1)
+    blocks = -(-int(channels) // 256)
+    while tile < 128 and -(-int(tokens) // tile) * blocks > _SEQ_CONV_RESIDENT:
+        tile *= 2
+    return tile
 MATRIX_MEMORY_MAX_DIM = 256
 
 

@@ -72,7 +72,8 @@ class ConvQKV:
         if heads.kv_heads:
             kv = (pool, table, ctx.page_size, heads.kv_heads, heads.head_dim, heads.v_dim or heads.head_dim)
         q = ops.seq_conv(qkv[:, :C], taps, None, ctx.states.get((call, "qkv_conv")), ctx.cu_seqlens, ctx.seq_ctx,
-                         ctx.seq_slot, ctx.tiles(self.tile), qkv.dtype, out_channels=nq, kv=kv)
+                         ctx.seq_slot, ctx.tiles(ops.seq_conv_tile(self.tile, qkv.shape[0], C)), qkv.dtype,
+                         out_channels=nq, kv=kv)
         return q.view(-1, heads.heads, heads.head_dim)
 
 

@@ -53,7 +53,8 @@ class ParallelBlock:
             # storage type
             x, x32, stream = self.norm.add_norm(h, residual, pending, wide=True)
             xm = ops.seq_conv(x32, self.taps, None, ctx.states.get((call, "canon")), ctx.cu_seqlens, ctx.seq_ctx,
-                              ctx.seq_slot, ctx.tiles(self.tile), self.norm.store, residual=True)
+                              ctx.seq_slot, ctx.tiles(ops.seq_conv_tile(self.tile, x32.shape[0], self.norm.width)),
+                              self.norm.store, residual=True)
         y = self.mixer.forward(xm, ctx, call)
         if self.ffn is None:
             return y, stream, None

@@ -69,7 +69,7 @@ class GatedLinearRecurrence:
         W, T = self.width, x.shape[0]
         proj = self.in_proj(x)                                    # [T, y | x]
         u = ops.seq_conv(proj[:, W:], self.conv, self.conv_bias, ctx.states.get((call, "conv")), ctx.cu_seqlens,
-                         ctx.seq_ctx, ctx.seq_slot, ctx.tiles(self.tile), proj.dtype)
+                         ctx.seq_ctx, ctx.seq_slot, ctx.tiles(ops.seq_conv_tile(self.tile, T, W)), proj.dtype)
         ub = u.view(T, self.blocks, W // self.blocks).transpose(0, 1)          # [blocks, T, w]
         if u.dtype == torch.float32:
             z = ops.gemm_batched(ub, self.gates)                               # 32-bit FMA
