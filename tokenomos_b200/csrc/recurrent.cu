@@ -208,7 +208,7 @@ TK_API int tk_rglru_scan(const float* z, int Tz, const float* rb, const float* i
 // ---------------------------------------------------------------------------------------------
 // 2. matrix memory: one warp per (sequence, head, group of CW columns of [S | n]); a lane holds
 // the rows d = lane + 32 j of its columns. The state is kept [head, column, d] so that a warp's
-// reads and writes of it are contiguous. A block's warps share a head: they stage MTC tokens of
+// reads and writes of it are contiguous. A block's warps share a head: they stage 32 (16) tokens of
 // q, k and their columns of v in shared memory together (the next round's loads are in flight
 // while this round is walked). Each warp forms the round's gates with a lane per token: the
 // running maximum m -> max(f + m, i) is a scan over maps of that form, which compose as
@@ -219,9 +219,8 @@ TK_API int tk_rglru_scan(const float* z, int Tz, const float* rb, const float* i
 namespace {
 constexpr int CW = 4;        // columns per warp
 constexpr int MWARPS = 4;    // warps per block
-constexpr int MTC = 16;      // tokens staged per round
 constexpr int MSB = 8;       // tokens reduced together: MSB * CW = 32 partial sums a lane
-static_assert(MSB * CW == 32 && MTC % MSB == 0, "one total per lane");
+static_assert(MSB * CW == 32, "one total per lane");
 }
 
 template <typename T, int DPL>
@@ -230,6 +229,8 @@ mlstm_scan_kernel(const T* qkv, int64_t stride, int q_off, int k_off, int v_off,
                   float cap, float q_scale, float* S_state, const float* m_state, const int* cu_seqlens,
                   const int* seq_ctx, const int* seq_slot, float* num, float* m_out, int H, int dim, int vd) {
     constexpr int DP = 32 * DPL;                          // the key size, padded
+    constexpr int MTC = DPL <= 4 ? 32 : 16;               // tokens staged per round (what shared memory holds)
+    static_assert(MTC % MSB == 0 && MTC <= 32, "a lane per token of a round");
     constexpr int NE = MTC * DP / (32 * MWARPS);          // elements of q (and of k) a thread stages per round
     constexpr int NV = MTC * MWARPS * CW / (32 * MWARPS); // and of v
     __shared__ float q_s[MTC][DP], k_s[MTC][DP];

@@ -36,11 +36,22 @@ seq_conv_kernel(const TI* in, int64_t in_stride, const float* __restrict__ taps,
                 PagedDest dest) {
     pdl_launch_dependents();
     pdl_wait();
-    const int n = tile_n[blockIdx.x];
+    // The walk is bound by the latency of dependent loads, so they are asked for as early as their
+    // addresses are known: the tile's four numbers together, then the tile's first inputs and the
+    // inputs before it beside the sequence's numbers (only the choice between those inputs and the
+    // state needs the sequence's context).
+    constexpr int AHEAD = 8;                          // inputs in flight
+    const int n = tile_n[blockIdx.x], s = tile_seq[blockIdx.x], tok0 = tile_tok0[blockIdx.x], off = tile_off[blockIdx.x];
     if (n <= 0) return;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    const int s = tile_seq[blockIdx.x], tok0 = tile_tok0[blockIdx.x], off = tile_off[blockIdx.x];
+    float ahead[AHEAD];
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) ahead[k] = to_f<TI>(in[(size_t)(tok0 + min(k, n - 1)) * in_stride + c]);
+    float before[MAX_TAPS];                           // before[d - 1]: the input d tokens back within the portion
+#pragma unroll
+    for (int d = 1; d < MAX_TAPS; ++d)
+        before[d - 1] = (d < K && off - d >= 0) ? to_f<TI>(in[(size_t)(tok0 - d) * in_stride + c]) : 0.f;
     const int ctx = seq_ctx[s];
     const int pos0 = ctx + off;                       // position of the tile's first token
     float w[MAX_TAPS], past[MAX_TAPS];                // past[d - 1]: the input d positions back
@@ -61,7 +72,7 @@ seq_conv_kernel(const TI* in, int64_t in_stride, const float* __restrict__ taps,
     for (int d = 1; d < MAX_TAPS; ++d) {
         float v = 0.f;
         if (d < K && pos0 - d >= 0) {
-            if (off - d >= 0) v = to_f<TI>(in[(size_t)(tok0 - d) * in_stride + c]);
+            if (off - d >= 0) v = before[d - 1];
             else v = old[K - 1 - d];                  // off == 0 (tiles are >= K - 1 long) and ctx > 0
         }
         past[d - 1] = v;
@@ -78,11 +89,12 @@ seq_conv_kernel(const TI* in, int64_t in_stride, const float* __restrict__ taps,
         page_part = ((size_t)which * dest.Hkv + e / D) * dest.P * dest.Dp + e % D;
     }
     const size_t page_size = (size_t)2 * dest.Hkv * dest.P * dest.Dp;
-    constexpr int AHEAD = 8;                           // inputs in flight: the walk is bound by their latency
     for (int i0 = 0; i0 < n; i0 += AHEAD) {
-        float ahead[AHEAD];
+        if (i0 > 0) {
 #pragma unroll
-        for (int k = 0; k < AHEAD; ++k) ahead[k] = to_f<TI>(in[(size_t)(tok0 + min(i0 + k, n - 1)) * in_stride + c]);
+            for (int k = 0; k < AHEAD; ++k)
+                ahead[k] = to_f<TI>(in[(size_t)(tok0 + min(i0 + k, n - 1)) * in_stride + c]);
+        }
 #pragma unroll
         for (int k = 0; k < AHEAD; ++k) {
             const int i = i0 + k;

@@ -1161,6 +1161,8 @@ def seq_conv_tile(base: int, tokens: int, channels: int) -> int:
     while tile < 128 and -(-int(tokens) // tile) * blocks > _SEQ_CONV_RESIDENT:
         tile *= 2
     return tile
+
+
 MATRIX_MEMORY_MAX_DIM = 256
 
 
