@@ -338,6 +338,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 
 // GM: rows of a tile (64: 8 warps of 32 x 32; 128: 8 warps of 64 x 32); GSTAGES: copies in flight.
 // gate (batched form only): C[g][m][:] *= sigmoid(gate[m * gate_stride + g]).
+// act 1: relu(v)^2. act 2: the weight's rows are gates and ups alternating in runs of 8; C has N / 2
+// columns, silu(gate) * up.
 // GN: columns of a tile (128, or 64 for steps of a few rows: twice the CTAs to stream the weights).
 template <int GM, int GSTAGES, int GN>
 __global__ void __launch_bounds__(G_THREADS)
@@ -433,6 +435,26 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
             const int m = m0 + wm + i * 16 + (lane >> 2) + half * 8;
             if (m >= M) continue;
             const float gv = gate != nullptr ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)m * gate_stride + gz]))) : 1.0f;
+            if (act == 2) {
+                // gate and up rows of the weight alternate in runs of 8: a warp's n8 blocks 2 jj and
+                // 2 jj + 1 are the gates and the ups of the same eight units, in the same lanes.
+                // Both are rounded to the storage type first, as a product that is stored would be.
+#pragma unroll
+                for (int jj = 0; jj < NJ / 2; ++jj) {
+                    const int n = n0 + wn + jj * 16 + (lane & 3) * 2;
+                    if (n >= N) continue;
+                    float y[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float g = __bfloat162float(__float2bfloat16_rn(acc[i][2 * jj][half * 2 + e]));
+                        const float u = __bfloat162float(__float2bfloat16_rn(acc[i][2 * jj + 1][half * 2 + e]));
+                        y[e] = g / (1.f + expf(-g)) * u * gv;
+                    }
+                    *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + (n >> 4) * 8 + (lane & 3) * 2) =
+                        __floats2bfloat162_rn(y[0], y[1]);
+                }
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
                 const int n = n0 + wn + j * 8 + (lane & 3) * 2;
@@ -460,7 +482,7 @@ TK_API int tk_gemm_grouped_mma(const void* A, int64_t lda, int64_t a_gs, const i
                  "gemm_grouped_mma: K, N and the strides must be whole 16-byte chunks");
     TK_CHECK_ARG(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)C % 4) == 0,
                  "gemm_grouped_mma: operands must be 16-byte aligned");
-    TK_CHECK_ARG(act == 0 || act == 1, "gemm_grouped_mma: activation %d", act);
+    TK_CHECK_ARG(act == 0 || act == 1 || (act == 2 && N % 16 == 0), "gemm_grouped_mma: activation %d with %d columns", act, N);
     if (M == 0) return 0;
     // few row tiles (a step of a few tokens streams the weights): columns in tiles of 64, so that
     // twice as many CTAs share the stream and an SM holds four of them

@@ -1065,13 +1065,24 @@ def gemm_grouped_tiles(a_dtype: torch.dtype, n: int, k: int, rows: int) -> int:
 
 
 def gemm_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row_index: torch.Tensor | None,
-                 rows: int, act: bool = False, tile: int = 64) -> torch.Tensor:
+                 rows: int, act: bool | str = False, tile: int = 64) -> torch.Tensor:
     """``out[m] = act(a[row_index[m]] @ w[g].T)`` with ``g = tile_group[m // tile]``; ``w`` [G, N, K];
-    a row index of -1 reads zeros, a tile group of -1 is skipped (its rows are not written)."""
+    a row index of -1 reads zeros, a tile group of -1 is skipped (its rows are not written). ``act``
+    True: ``relu(v)^2``; ``"swiglu8"`` (tensor-core form only, see ``gemm_grouped_fuses_swiglu``): the
+    rows of ``w[g]`` are gate and up rows alternating in runs of 8 and ``out`` [rows, N / 2] is
+    ``silu(gate) * up``."""
     _cuda(a, w, tile_group, row_index)
     G, N, K = w.shape
     if a.dtype != w.dtype or a.stride(1) != 1 or not w.is_contiguous() or a.shape[1] != K:
         raise KernelError(f"gemm_grouped: a {tuple(a.shape)} {a.dtype} against w {tuple(w.shape)} {w.dtype}")
+    if act == "swiglu8":
+        if not gemm_grouped_fuses_swiglu(a, w):
+            raise KernelError("gemm_grouped: the gated activation in the epilogue is the tensor-core form's")
+        out = torch.empty(rows, N // 2, dtype=a.dtype, device=a.device)
+        _lib.call("tk_gemm_grouped_mma", _ptr(a), a.stride(0), 0, _ptr(row_index), _ptr(w), K, N * K,
+                  _ptr(_i32(tile_group, "tile_group")), _ptr(out), N // 2, 0, rows, N, K, G, 2, int(tile), None, 0,
+                  _stream())
+        return out
     out = torch.empty(rows, N, dtype=a.dtype, device=a.device)
     if _grouped_mma_ok(a, w, N, K):
         _lib.call("tk_gemm_grouped_mma", _ptr(a), a.stride(0), 0, _ptr(row_index), _ptr(w), K, N * K,
@@ -1084,6 +1095,12 @@ def gemm_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row
               _ptr(_i32(tile_group, "tile_group")), _ptr(out), N, 0, rows, N, K, G, int(bool(act)), _dtype_code(a),
               _stream())
     return out
+
+
+def gemm_grouped_fuses_swiglu(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_grouped(a, w, ..., act="swiglu8")`` is built for these operands."""
+    N, K = w.shape[-2:]
+    return N % 16 == 0 and _grouped_mma_ok(a, w, N, K)
 
 
 def _grouped_mma_ok(a: torch.Tensor, w: torch.Tensor, N: int, K: int) -> bool:

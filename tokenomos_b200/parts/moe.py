@@ -32,14 +32,21 @@ class RoutedExperts:
         """``up`` [E, ff, width], ``down`` [E, width, ff]; ``router`` [E (+ 1 if ``shared_gate``) (+ zero
         rows), width] (it may carry a bias). ``activation`` "relu2": ``act(v) = relu(v)^2``; "swiglu": an
         expert is ``W_down (silu(W_gate h) * (W_up h))`` and ``up`` holds each expert's gate rows, then its
-        up rows ([E, 2 ff, width])."""
+        up rows ([E, 2 ff, width]; kept with gate and up alternating in runs of 8 where the kernels
+        take that)."""
         if activation not in ("relu2", "swiglu"):
             raise ValueError(f"mixture of experts: activation {activation!r}: 'relu2' or 'swiglu'")
         self.activation = activation
-        self.router, self.up, self.down = router, up.contiguous(), down.contiguous()
         self.experts, self.ff, self.width = up.shape
+        self.gate_run = 0
         if activation == "swiglu":
             self.ff //= 2
+            if up.dtype == torch.bfloat16 and self.ff % 8 == 0:
+                # gate and up rows alternating in runs of 8: the tensor-core product then has a unit's
+                # gate and up in one thread and applies the activation in its epilogue
+                self.gate_run = 8
+                up = up.reshape(self.experts, 2, self.ff // 8, 8, self.width).transpose(1, 2).reshape(up.shape)
+        self.router, self.up, self.down = router, up.contiguous(), down.contiguous()
         self.top, self.scale = int(top), float(scale)
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"mixture of experts: {self.top} of {self.experts} experts per token")
@@ -69,8 +76,10 @@ class RoutedExperts:
                                       x.shape[0] * self.top)
         row_token, pair_row, tile_expert = ops.moe_sort(idx, self.experts, tile)
         rows = row_token.numel()
-        if self.activation == "swiglu":
-            act = ops.swiglu(ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, tile=tile))
+        if self.activation == "swiglu" and self.gate_run and ops.gemm_grouped_fuses_swiglu(x, self.up):
+            act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act="swiglu8", tile=tile)
+        elif self.activation == "swiglu":
+            act = ops.swiglu(ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, tile=tile), self.gate_run)
         else:
             act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act=True, tile=tile)
         y = ops.gemm_grouped(act, self.down, tile_expert, None, rows, tile=tile)
@@ -87,7 +96,7 @@ class RoutedExperts:
         row_token, pair_row, _, ends = ops.moe_sort(idx, self.experts, 8, ends=True)
         rows = ops.gather_rows_or_zero(x, row_token)
         act = torch._grouped_mm(rows, self.up.transpose(1, 2), offs=ends)
-        act = ops.swiglu(act) if self.activation == "swiglu" else ops.relu2(act)
+        act = ops.swiglu(act, self.gate_run) if self.activation == "swiglu" else ops.relu2(act)
         return torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends), pair_row
 
 
