@@ -744,6 +744,41 @@ def test_gated_experts_alone(dtype, E, top, ff, T, tmp_path):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("E, ff, width, T, top", [(5, 24, 40, 37, 2), (3, 64, 128, 130, 3), (9, 8, 16, 3, 4)])
+def test_gated_activation_in_the_grouped_products_epilogue(E, ff, width, T, top):
+    """``silu(gate) * up`` inside the grouped product (gate and up rows alternating in runs of 8)
+    against the same weights' plain products in float64: gathered rows, rows of zeros, tiles that no
+    expert owns, several column tiles."""
+    from tokenomos_b200 import ops
+
+    g = torch.Generator().manual_seed(E * 100 + ff)
+    x = torch.randn(T, width, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(E, ff, width, generator=g) * 0.3).to(torch.bfloat16)
+    up = (torch.randn(E, ff, width, generator=g) * 0.3).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    runs = torch.stack((gate.view(E, ff // 8, 8, width), up.view(E, ff // 8, 8, width)), dim=2).reshape(E, 2 * ff, width)
+    xd, wd = x.cuda(), runs.contiguous().cuda()
+    assert ops.gemm_grouped_fuses_swiglu(xd, wd)
+    tile = ops.gemm_grouped_tiles(torch.bfloat16, ff, ff, T * top)
+    row_token, pair_row, tile_expert = ops.moe_sort(idx.cuda(), E, tile)
+    got = ops.gemm_grouped(xd, wd, tile_expert, row_token, row_token.numel(), act="swiglu8", tile=tile)
+    assert tuple(got.shape) == (row_token.numel(), ff)
+    got = got.double().cpu()
+    rows, owner = row_token.cpu(), tile_expert.cpu()
+    checked = 0
+    for r in range(rows.numel()):
+        e, t = int(owner[r // tile]), int(rows[r])
+        if e < 0:
+            continue                      # a tile of the fixed-size layout that no expert owns: not written
+        h = x[t].double() if t >= 0 else torch.zeros(width, dtype=torch.float64)
+        a, b = gate[e].double() @ h, up[e].double() @ h
+        want = a / (1 + torch.exp(-a)) * b
+        assert (got[r] - want).abs().max() <= 2e-2 * max(1.0, want.abs().max().item()), (r, e, t)
+        checked += t >= 0
+    assert checked == T * top
+
+
+@pytest.mark.gpu
 def test_router_takes_the_lowest_index_of_equal_logits(tmp_path):
     width = 32
     layer = dict(mlstm(1, 8, 8, 5.0), mlp=moe(6, 2, 16))
