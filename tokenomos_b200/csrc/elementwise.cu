@@ -554,9 +554,9 @@ TK_API int tk_scale_rows_f32(const void* x, int64_t ld, float* out, float scale,
     return 0;
 }
 
-// logits [rows, vocab] float32, in place: cap > 0: x = cap * tanh(x / cap); then the `n_suppress`
-// ids of `suppress` (each inside the vocabulary) become -inf in every row
-__global__ void logit_options_kernel(float* logits, int64_t ld, int rows, int vocab, float cap,
+// logits [rows, vocab] float32, in place: x = x * scale; cap > 0: x = cap * tanh(x / cap); then the
+// `n_suppress` ids of `suppress` (each inside the vocabulary) become -inf in every row
+__global__ void logit_options_kernel(float* logits, int64_t ld, int rows, int vocab, float scale, float cap,
                                      const int* suppress, int n_suppress) {
     pdl_launch_dependents();
     pdl_wait();
@@ -569,20 +569,21 @@ __global__ void logit_options_kernel(float* logits, int64_t ld, int rows, int vo
         bool hit = false;
         for (int k = 0; k < n_suppress; ++k) hit = hit || suppress[k] == col;
         if (hit) *at = -INFINITY;
-        else if (cap > 0.f) *at = cap * tanhf(*at * inv);
+        else if (cap > 0.f) *at = cap * tanhf(*at * scale * inv);
+        else *at = *at * scale;
     }
 }
 
-TK_API int tk_logit_options(float* logits, int64_t ld, int rows, int vocab, float cap, const int* suppress,
-                            int n_suppress, cudaStream_t stream) {
+TK_API int tk_logit_options(float* logits, int64_t ld, int rows, int vocab, float scale, float cap,
+                            const int* suppress, int n_suppress, cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && vocab > 0 && ld >= vocab && n_suppress >= 0, "logit_options: bad sizes");
     TK_CHECK_ARG(n_suppress == 0 || suppress != nullptr, "logit_options: the suppress list is missing");
-    if (rows == 0 || (cap <= 0.f && n_suppress == 0)) return 0;
+    if (rows == 0 || (cap <= 0.f && n_suppress == 0 && scale == 1.0f)) return 0;
     const int threads = 256;
     const int64_t want = ((int64_t)rows * vocab + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    tk_launch(logit_options_kernel, dim3(blocks), dim3(threads), 0, stream, logits, ld, rows, vocab, cap, suppress,
-              n_suppress);
+    tk_launch(logit_options_kernel, dim3(blocks), dim3(threads), 0, stream, logits, ld, rows, vocab, scale, cap,
+              suppress, n_suppress);
     TK_CHECK_LAUNCH("logit_options");
     return 0;
 }

@@ -56,6 +56,7 @@ latent_prepare_kernel(const T* proj, int64_t proj_stride, const float* __restric
             cq_out[(size_t)t * Rq + i] = from_f<T>(to_f<T>(row[i]) * rq * wq[i]);
         return;
     }
+    if (cache == nullptr) return;        // the layer reads another layer's latents: queries only
     float* cs = smem;
     float* sn = smem + rot / 2;
     const int pos = positions[t];

@@ -2,6 +2,7 @@
 //
 //     y_t[c] = (residual ? u_t[c] : 0) + bias[c] + sum_j taps[c, j] * u_(t - K + 1 + j)[c]
 //
+// (`act` 1: y <- silu(y), formed in 32-bit before the one rounding)
 // within each sequence, zeros before its start; the last K - 1 inputs u of every sequence are the
 // request's state (float32 [slots, K - 1, C]; a 16-bit input widens exactly). The input rows may
 // be a column block of a wider tensor (a fused projection). The channels from `c_paged` on do not
@@ -32,8 +33,8 @@ __global__ void __launch_bounds__(256)
 seq_conv_kernel(const TI* in, int64_t in_stride, const float* __restrict__ taps, const float* __restrict__ bias,
                 float* state, const int* cu_seqlens, const int* seq_ctx, const int* seq_slot,
                 const int* tile_seq, const int* tile_tok0, const int* tile_off, const int* tile_n, TO* out,
-                int64_t out_stride, TO* plain, int64_t plain_stride, int K, int C, int residual, int c_paged,
-                PagedDest dest) {
+                int64_t out_stride, TO* plain, int64_t plain_stride, int K, int C, int residual, int act,
+                int c_paged, PagedDest dest) {
     pdl_launch_dependents();
     pdl_wait();
     // The walk is bound by the latency of dependent loads, so they are asked for as early as their
@@ -105,6 +106,7 @@ seq_conv_kernel(const TI* in, int64_t in_stride, const float* __restrict__ taps,
 #pragma unroll
             for (int d = 1; d < MAX_TAPS; ++d)
                 if (d < K) acc = fmaf(w[K - 1 - d], past[d - 1], acc);
+            if (act) acc = acc / (1.0f + expf(-acc));
             if (paged) {
                 const int pos = pos0 + i;
                 const int page = TK_PAGE(TK_K_SEQ_CONV, dest.block_table[(size_t)s * dest.bt_stride + pos / dest.P]);
@@ -142,8 +144,8 @@ TK_API int tk_seq_conv(const void* in, int64_t in_stride, int in_dtype, const fl
                        float* state, const int* cu_seqlens, const int* seq_ctx, const int* seq_slot,
                        const int* tile_seq, const int* tile_tok0, const int* tile_off, const int* tile_n,
                        int n_tiles, void* out, int64_t out_stride, void* plain, int64_t plain_stride, int out_dtype,
-                       int K, int C, int residual, int c_paged, void* pool, const int* block_table, int bt_stride,
-                       int P, int Hkv, int Dk, int Dv, int Dp, cudaStream_t stream) {
+                       int K, int C, int residual, int act, int c_paged, void* pool, const int* block_table,
+                       int bt_stride, int P, int Hkv, int Dk, int Dv, int Dp, cudaStream_t stream) {
     TK_CHECK_ARG(K >= 1 && K <= MAX_TAPS, "sequence conv: %d taps; 1..%d are built", K, MAX_TAPS);
     TK_CHECK_ARG(K == 1 || state != nullptr, "sequence conv: %d taps need a state", K);
     TK_CHECK_ARG(C > 0 && n_tiles >= 0, "sequence conv: bad sizes");
@@ -162,7 +164,7 @@ TK_API int tk_seq_conv(const void* in, int64_t in_stride, int in_dtype, const fl
 #define TK_SC(TI, TO)                                                                                       \
     tk_launch(seq_conv_kernel<TI, TO>, grid, dim3(256), 0, stream, (const TI*)in, in_stride, taps, bias,    \
               state, cu_seqlens, seq_ctx, seq_slot, tile_seq, tile_tok0, tile_off, tile_n, (TO*)out,        \
-              out_stride, (TO*)plain, plain_stride, K, C, residual, c_paged, dest)
+              out_stride, (TO*)plain, plain_stride, K, C, residual, act, c_paged, dest)
     if (in_dtype == TK_F32 && out_dtype == TK_F32) TK_SC(float, float);
     else if (in_dtype == TK_F32 && out_dtype == TK_BF16) TK_SC(float, __nv_bfloat16);
     else if (in_dtype == TK_BF16 && out_dtype == TK_BF16) TK_SC(__nv_bfloat16, __nv_bfloat16);

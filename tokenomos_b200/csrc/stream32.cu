@@ -320,3 +320,149 @@ TK_API int tk_sigmoid_gate(void* x, const void* g, int64_t ldg, int rows, int wi
     TK_CHECK_LAUNCH("sigmoid_gate");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The stream's add with a norm in groups, and a gate on what is added:
+//   stream' = stream + x * sigmoid(gate)      (x optional; gate optional: the plain add)
+//   y = T(stream' / sqrt(mean_group(stream'^2) + eps) * w)
+// The row is split into `groups` equal consecutive parts, each divided by its own root mean square.
+// One warp per (row, group); a lane keeps its elements in registers when the group is short enough
+// (ITEMS per lane: 4 elements at a time where VEC, which wants the group a multiple of 4 and every
+// row 16-byte aligned), else it reads its own writes back from stream_out.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int ITEMS, bool VEC>
+__global__ void __launch_bounds__(128)
+stream32_group_norm_kernel(const float* stream_in, const T* x, int64_t x_stride, const T* gate, int64_t gate_stride,
+                           const float* __restrict__ w, float eps, float* stream_out, T* y, int rows, int width,
+                           int groups) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (warp >= rows * groups) return;
+    const int gw = width / groups, c0 = (warp % groups) * gw;
+    const size_t r = warp / groups;
+    if constexpr (VEC) {
+        float4 keep[ITEMS];
+        float4 a[ITEMS], b[ITEMS], g[ITEMS];
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+            const int i = (lane + 32 * k) * 4;
+            a[k] = b[k] = g[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < gw) {
+                if (stream_in != nullptr) a[k] = *reinterpret_cast<const float4*>(stream_in + r * width + c0 + i);
+                if (x != nullptr) b[k] = Quad<T>::load(x + r * x_stride + c0 + i);
+                if (gate != nullptr) g[k] = Quad<T>::load(gate + r * gate_stride + c0 + i);
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+            const int i = (lane + 32 * k) * 4;
+            float4 v = a[k];
+            if (x != nullptr) {
+                if (gate != nullptr) {
+                    b[k].x /= 1.0f + expf(-g[k].x), b[k].y /= 1.0f + expf(-g[k].y);
+                    b[k].z /= 1.0f + expf(-g[k].z), b[k].w /= 1.0f + expf(-g[k].w);
+                }
+                v = make_float4(v.x + b[k].x, v.y + b[k].y, v.z + b[k].z, v.w + b[k].w);
+            }
+            if (i < gw && stream_out != nullptr) *reinterpret_cast<float4*>(stream_out + r * width + c0 + i) = v;
+            keep[k] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        if (w == nullptr) return;
+        const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)gw + eps);
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+            const int i = (lane + 32 * k) * 4;
+            if (i < gw) {
+                const float4 q = *reinterpret_cast<const float4*>(w + c0 + i);
+                Quad<T>::store(y + r * width + c0 + i, make_float4(keep[k].x * rstd * q.x, keep[k].y * rstd * q.y,
+                                                                   keep[k].z * rstd * q.z, keep[k].w * rstd * q.w));
+            }
+        }
+    } else {
+        auto sum_at = [&](int i) {
+            float v = stream_in != nullptr ? stream_in[r * width + c0 + i] : 0.f;
+            if (x != nullptr) {
+                float add = to_f<T>(x[r * x_stride + c0 + i]);
+                if (gate != nullptr) add /= 1.0f + expf(-to_f<T>(gate[r * gate_stride + c0 + i]));
+                v += add;
+            }
+            if (stream_out != nullptr) stream_out[r * width + c0 + i] = v;
+            return v;
+        };
+        float ss = 0.f;
+        if constexpr (ITEMS > 0) {
+            float keep[ITEMS];
+#pragma unroll
+            for (int k = 0; k < ITEMS; ++k) {
+                const int i = lane + 32 * k;
+                keep[k] = i < gw ? sum_at(i) : 0.f;
+                ss += keep[k] * keep[k];
+            }
+            if (w == nullptr) return;
+            const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)gw + eps);
+#pragma unroll
+            for (int k = 0; k < ITEMS; ++k) {
+                const int i = lane + 32 * k;
+                if (i < gw) y[r * width + c0 + i] = from_f<T>(keep[k] * rstd * w[c0 + i]);
+            }
+        } else {
+            for (int i = lane; i < gw; i += 32) {
+                const float v = sum_at(i);
+                ss += v * v;
+            }
+            if (w == nullptr) return;
+            const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)gw + eps);
+            for (int i = lane; i < gw; i += 32)
+                y[r * width + c0 + i] = from_f<T>(stream_out[r * width + c0 + i] * rstd * w[c0 + i]);
+        }
+    }
+}
+
+template <typename T>
+static void launch_group_norm(const float* stream_in, const void* x, int64_t x_stride, const void* gate,
+                              int64_t gate_stride, const float* w, float eps, float* stream_out, void* y, int rows,
+                              int width, int groups, cudaStream_t stream) {
+    const int gw = width / groups;
+    const int warps = rows * groups;
+    dim3 grid((warps + 3) / 4), block(128);
+    auto aligned = [](const void* p, int to) { return ((uintptr_t)p & (to - 1)) == 0; };
+    const int tb = sizeof(T) == 2 ? 8 : 16;
+    const bool vec = gw % 4 == 0 && x_stride % 4 == 0 && gate_stride % 4 == 0 && aligned(stream_in, 16) &&
+                     aligned(stream_out, 16) && aligned(w, 16) && aligned(x, tb) && aligned(gate, tb) && aligned(y, tb);
+#define TK_GN(ITEMS, VEC)                                                                                          \
+    tk_launch(stream32_group_norm_kernel<T, ITEMS, VEC>, grid, block, 0, stream, stream_in, (const T*)x, x_stride,  \
+              (const T*)gate, gate_stride, w, eps, stream_out, (T*)y, rows, width, groups)
+    if (vec && gw <= 128 * 2) TK_GN(2, true);
+    else if (vec && gw <= 128 * 8) TK_GN(8, true);
+    else if (gw <= 32 * 8) TK_GN(8, false);
+    else TK_GN(0, false);
+#undef TK_GN
+}
+
+// stream_in / stream_out: float [rows, width] (may be the same buffer; stream_out may be null only when
+// a group fits the register path, gw <= 256 or, 16-byte aligned, 1024); x, gate: T rows `x_stride` /
+// `gate_stride` elements apart; w: float [width] or null (the add alone).
+TK_API int tk_stream32_group_norm(const float* stream_in, const void* x, int64_t x_stride, const void* gate,
+                                  int64_t gate_stride, const float* w, float eps, float* stream_out, void* y, int rows,
+                                  int width, int groups, int dtype, cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && width > 0 && groups > 0 && width % groups == 0,
+                 "stream32_group_norm: a row of %d in %d groups", width, groups);
+    TK_CHECK_ARG(stream_in != nullptr || x != nullptr, "stream32_group_norm: nothing to add up");
+    TK_CHECK_ARG(gate == nullptr || x != nullptr, "stream32_group_norm: a gate without rows to gate");
+    TK_CHECK_ARG(stream_out != nullptr, "stream32_group_norm: no stream to write");
+    TK_CHECK_ARG(w == nullptr || y != nullptr, "stream32_group_norm: a norm weight without an output");
+    if (rows == 0) return 0;
+    if (dtype == TK_F32)
+        launch_group_norm<float>(stream_in, x, x_stride, gate, gate_stride, w, eps, stream_out, y, rows, width, groups,
+                                 stream);
+    else if (dtype == TK_BF16)
+        launch_group_norm<__nv_bfloat16>(stream_in, x, x_stride, gate, gate_stride, w, eps, stream_out, y, rows, width,
+                                         groups, stream);
+    else
+        TK_CHECK_ARG(false, "stream32_group_norm: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("stream32_group_norm");
+    return 0;
+}

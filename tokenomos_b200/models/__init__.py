@@ -15,6 +15,7 @@ from pathlib import Path
 import torch
 
 from tokenomos_b200.models.darizen import Darizen
+from tokenomos_b200.models.fakelorn import Fakelorn
 from tokenomos_b200.models.laposun import Laposun
 from tokenomos_b200.models.lfm3 import Lfm3
 from tokenomos_b200.models.lisorax import Lisorax
@@ -97,3 +98,4 @@ register(Lfm3())
 register(Darizen())
 register(Laposun())
 register(Lisorax())
+register(Fakelorn())

@@ -147,15 +147,17 @@ def scale_rows(x: torch.Tensor, scale: float) -> torch.Tensor:
     return x
 
 
-def logit_options(logits: torch.Tensor, softcap: float | None, suppress: torch.Tensor | None) -> torch.Tensor:
-    """In place on float32 ``logits`` [rows, vocab]: ``softcap * tanh(logits / softcap)`` if a cap
-    is given, then ``-inf`` at the token ids of ``suppress`` (int32, each inside the vocabulary)."""
+def logit_options(logits: torch.Tensor, softcap: float | None, suppress: torch.Tensor | None,
+                  scale: float | None = None) -> torch.Tensor:
+    """In place on float32 ``logits`` [rows, vocab]: times ``scale`` if one is given, ``softcap *
+    tanh(logits / softcap)`` if a cap is given, then ``-inf`` at the token ids of ``suppress`` (int32,
+    each inside the vocabulary)."""
     _cuda(logits, suppress)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("logit_options: logits must be float32 [rows, vocab] with contiguous rows")
     n = 0 if suppress is None else _i32(suppress, "suppress").numel()
     _lib.call("tk_logit_options", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1],
-              float(softcap or 0.0), _ptr(suppress), n, _stream())
+              1.0 if scale is None else float(scale), float(softcap or 0.0), _ptr(suppress), n, _stream())
     return logits
 
 
@@ -892,14 +894,23 @@ def canon_conv(h: torch.Tensor, taps: torch.Tensor, state: torch.Tensor | None, 
 # ---- attention over a cache of latents ----------------------------------------------------------
 
 def latent_prepare(proj: torch.Tensor, wq: torch.Tensor, wkv: torch.Tensor, eps: float, freq: torch.Tensor,
-                   positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, cache: torch.Tensor,
-                   q_rank: int, rank: int, rot_dim: int) -> torch.Tensor:
+                   positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor | None,
+                   cache: torch.Tensor | None, q_rank: int, rank: int, rot_dim: int) -> torch.Tensor:
     """From the down-projection's rows ``[q latent | kv latent | rotated key part | ...]``: the normed
     query latent [T, q_rank] (returned), and into ``cache`` [pages, P, rank + rot_dim], at each token's
     position, the normed kv latent and the key part rotated by ``position * freq`` (pairs (2i, 2i+1),
-    ``2 len(freq)`` columns)."""
+    ``2 len(freq)`` columns). ``cache`` None: the rows hold the query latent only (a layer that reads
+    another layer's cache)."""
     _cuda(proj, wq, wkv, freq, positions, tok_seq, block_table, cache)
     T = proj.shape[0]
+    if cache is None:
+        if proj.stride(1) != 1 or proj.shape[1] < q_rank:
+            raise KernelError("latent_prepare: projection rows are too short")
+        cq = torch.empty(T, q_rank, dtype=proj.dtype, device=proj.device)
+        _lib.call("tk_latent_prepare", _ptr(proj), proj.stride(0), _ptr(_f32vec(wq, "q latent norm", q_rank)), None,
+                  float(eps), _ptr(freq), _ptr(_i32(positions, "positions")), _ptr(_i32(tok_seq, "tok_seq")), None, 0,
+                  _ptr(cq), None, T, q_rank, rank, rot_dim, 2 * freq.numel(), 1, _dtype_code(proj), _stream())
+        return cq
     if proj.stride(1) != 1 or proj.shape[1] < q_rank + rank + rot_dim:
         raise KernelError("latent_prepare: projection rows are too short")
     if (cache.dim() != 3 or cache.shape[2] != rank + rot_dim or cache.dtype != proj.dtype
@@ -1198,12 +1209,12 @@ def scale_rows_f32(x: torch.Tensor, scale: float) -> torch.Tensor:
 def seq_conv(u: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor | None,
              cu_seqlens: torch.Tensor, seq_ctx: torch.Tensor, seq_slot: torch.Tensor, tiles: tuple,
              out_dtype: torch.dtype, residual: bool = False, plain: bool = False, out_channels: int | None = None,
-             kv: tuple | None = None):
+             kv: tuple | None = None, act: bool = False):
     """Causal convolution over time on each channel: ``y_t = [u_t +] bias + sum_j taps[:, j] u_(t - K + 1 + j)``
     within each sequence (zeros before its start). ``u`` [T, C] (rows may be strided), ``taps`` float32
     [C, K]; the last K - 1 rows of ``u`` of every sequence are kept in ``state`` (float32
     [slots, K - 1, C]). ``tiles``: ``ctx.tiles(size)`` with size >= K - 1. ``plain``: also returns ``u``
-    itself in ``out_dtype``. ``kv`` = ``(pool, block_table, page, kv_heads, k_dim, v_dim)``: the
+    itself in ``out_dtype``. ``act``: ``y <- silu(y)``. ``kv`` = ``(pool, block_table, page, kv_heads, k_dim, v_dim)``: the
     channels from ``out_channels`` on are ``kv_heads`` key heads then as many value heads and go into
     the paged pool at each token's position instead of the result."""
     _cuda(u, taps, bias, state, cu_seqlens, seq_ctx, seq_slot, *tiles)
@@ -1235,7 +1246,7 @@ def seq_conv(u: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | None, sta
               _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")),
               _ptr(_i32(seq, "tile_seq")), _ptr(_i32(tok0, "tile_tok0")), _ptr(_i32(off, "tile_off")),
               _ptr(_i32(n, "tile_n")), seq.numel(), _ptr(out), n_out, _ptr(same), n_out, code[out_dtype], K, C,
-              int(bool(residual)), n_out, _ptr(pool), _ptr(table), bt, int(P), int(hkv), int(dk), int(dv), int(dp),
+              int(bool(residual)), int(bool(act)), n_out, _ptr(pool), _ptr(table), bt, int(P), int(hkv), int(dk), int(dv), int(dp),
               _stream())
     return (out, same) if plain else out
 
@@ -1377,3 +1388,108 @@ def mlstm_norm_gate(num: torch.Tensor, m: torch.Tensor, m_state: torch.Tensor, w
               _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_slot, "seq_slot")), _ptr(out), T, H, vd, float(eps),
               F32 if out_dtype == torch.float32 else BF16, _stream())
     return out
+
+
+SSD_MAX_STATE = 256
+
+
+def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, cu_seqlens: torch.Tensor, seq_ctx: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
+             heads: int, v_dim: int, n_state: int, groups: int) -> torch.Tensor:
+    """The state-space recurrence over a step's tokens: ``dt = softplus(dt_raw + dt_bias)``, ``S_t = exp(-exp(a_log)
+    dt) S_(t-1) + dt B_t x_t^T``, ``y_t = S_t^T C_t + d_skip x_t`` per head. ``xbc`` [T, >= heads v_dim + 2 groups
+    n_state] (rows may be strided): x, then B, then C; ``dt_raw`` float32 [T, >= heads]; ``state`` float32 [slots,
+    heads, n_state, v_dim]. Returns ``y`` float32 [T, heads v_dim]."""
+    _cuda(xbc, dt_raw, dt_bias, a_log, d_skip, state)
+    T = xbc.shape[0]
+    if xbc.stride(1) != 1 or xbc.shape[1] < heads * v_dim + 2 * groups * n_state:
+        raise KernelError("ssd_scan: rows of x, B and C with contiguous columns")
+    if dt_raw.dtype != torch.float32 or dt_raw.stride(1) != 1 or dt_raw.shape[0] != T or dt_raw.shape[1] < heads:
+        raise KernelError(f"ssd_scan: dt is float32 [{T}, >= {heads}]")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, n_state, v_dim) or not state.is_contiguous():
+        raise KernelError(f"ssd_scan: the state is float32 [slots, {heads}, {n_state}, {v_dim}]")
+    y = torch.empty(T, heads * v_dim, dtype=torch.float32, device=xbc.device)
+    _lib.call("tk_ssd_scan", _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(_f32vec(dt_bias, "dt_bias", heads)),
+              _ptr(_f32vec(a_log, "A_log", heads)), _ptr(_f32vec(d_skip, "D", heads)), _ptr(state),
+              _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")),
+              int(n_seqs), _ptr(y), heads, v_dim, n_state, groups, _dtype_code(xbc), _stream())
+    return y
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, groups: int) -> torch.Tensor:
+    """``v = y * silu(z)``, each of the row's ``groups`` equal parts divided by its own ``sqrt(mean(v^2) + eps)``,
+    times ``weight``. ``y`` float32 [T, C], ``z`` [T, C] in the storage type (rows may be strided); returns
+    [T, C] in ``z``'s type."""
+    _cuda(y, z, weight)
+    T, C = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or z.stride(1) != 1 or tuple(z.shape) != (T, C):
+        raise KernelError("gated_group_norm: y float32 [T, C] contiguous, z [T, C] with contiguous columns")
+    out = torch.empty(T, C, dtype=z.dtype, device=y.device)
+    _lib.call("tk_gated_group_norm", _ptr(y), _ptr(z), z.stride(0), _ptr(_f32vec(weight, "norm weight", C)), float(eps),
+              _ptr(out), T, C, int(groups), _dtype_code(z), _stream())
+    return out
+
+
+def qkv_maps_write(qkv: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor | None,
+                   pool: torch.Tensor | None, heads: int, kv_heads: int, dim: int, v_dim: int, maps: int) -> torch.Tensor:
+    """From rows ``[q | k | v]`` (q: ``heads`` heads of ``maps`` parts of ``dim``; k: ``kv_heads`` heads likewise;
+    v: ``kv_heads`` heads of ``v_dim``) the queries [T, heads * maps, maps * dim], each map a head of the key's
+    width with zeros outside its part, and the keys and values into ``pool`` [pages, 2, kv_heads, P, row] at
+    each token's position (``pool`` None: queries only). Positions enter nowhere."""
+    _cuda(qkv, positions, tok_seq, block_table, pool)
+    T = qkv.shape[0]
+    need = heads * maps * dim + (kv_heads * (maps * dim + v_dim) if pool is not None else 0)
+    if qkv.stride(1) != 1 or qkv.shape[1] < need:
+        raise KernelError(f"qkv_maps_write: rows of at least {need} contiguous columns")
+    q = torch.empty(T, heads * maps, maps * dim, dtype=qkv.dtype, device=qkv.device)
+    P = dp = bt = 0
+    if pool is not None:
+        if (pool.dtype != qkv.dtype or not pool.is_contiguous() or pool.dim() != 5 or pool.shape[1] != 2
+                or pool.shape[2] != kv_heads):
+            raise KernelError(f"qkv_maps_write: the pool is {qkv.dtype} [pages, 2, {kv_heads}, P, row]")
+        P, dp, bt = pool.shape[3], pool.shape[4], _i32(block_table, "block_table").stride(0)
+    _lib.call("tk_qkv_maps_write", _ptr(qkv), qkv.stride(0), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(block_table), bt, _ptr(q), _ptr(pool), T, heads, kv_heads, dim, v_dim,
+              maps, P, dp, _dtype_code(qkv), _stream())
+    return q
+
+
+def diff_combine(a: torch.Tensor, lam: float, coef: float, eps: float) -> torch.Tensor:
+    """``a`` [T, 2 H, V], a head's two maps' outputs side by side -> [T, H, V]: ``o = a_1 - lam a_2``, divided by
+    ``sqrt(mean(o^2) + eps)`` over the head's values, times ``coef`` (32-bit, one rounding)."""
+    _cuda(a)
+    T, H2, V = a.shape
+    if not a.is_contiguous() or H2 % 2:
+        raise KernelError("diff_combine: a is contiguous [T, 2 H, V]")
+    out = torch.empty(T, H2 // 2, V, dtype=a.dtype, device=a.device)
+    _lib.call("tk_diff_combine", _ptr(a), _ptr(out), T * (H2 // 2), V, float(lam), float(coef), float(eps),
+              _dtype_code(a), _stream())
+    return out
+
+
+def stream32_group_norm(stream: torch.Tensor | None, x: torch.Tensor | None, gate: torch.Tensor | None,
+                        weight: torch.Tensor | None, eps: float, groups: int, out_dtype: torch.dtype,
+                        in_place: bool = False):
+    """``stream' = stream + x * sigmoid(gate)`` in 32-bit (``x`` without ``gate``: the plain add; ``stream`` None:
+    ``x`` starts it), ``y = stream'`` with each of the row's ``groups`` equal parts divided by its own ``sqrt(mean
+    + eps)``, times ``weight``, rounded once to ``out_dtype``. Returns ``(y, stream')``; ``y`` None without
+    ``weight``. ``in_place``: ``stream`` is updated instead of copied."""
+    _cuda(stream, x, gate, weight)
+    src = x if x is not None else stream
+    rows, width = src.shape
+    if stream is not None and (stream.dtype != torch.float32 or not stream.is_contiguous()):
+        raise KernelError("stream32_group_norm: the stream is contiguous float32")
+    for t in (x, gate):
+        if t is not None and (t.stride(1) != 1 or tuple(t.shape) != (rows, width)):
+            raise KernelError("stream32_group_norm: x and gate are [rows, width] with contiguous columns")
+    if x is not None and gate is not None and gate.dtype != x.dtype:
+        raise KernelError("stream32_group_norm: x and gate are of one type")
+    kind = x if x is not None else torch.empty(0, dtype=out_dtype)
+    if kind.dtype != out_dtype:
+        raise KernelError("stream32_group_norm: x and the normed rows are of one type")
+    new = stream if (in_place and stream is not None) else torch.empty(rows, width, dtype=torch.float32, device=src.device)
+    y = torch.empty(rows, width, dtype=out_dtype, device=src.device) if weight is not None else None
+    _lib.call("tk_stream32_group_norm", _ptr(stream), _ptr(x), x.stride(0) if x is not None else 0, _ptr(gate),
+              gate.stride(0) if gate is not None else 0, _ptr(_f32vec(weight, "norm weight", width)), float(eps),
+              _ptr(new), _ptr(y), rows, width, int(groups), F32 if out_dtype == torch.float32 else BF16, _stream())
+    return y, new

@@ -64,7 +64,7 @@ _SIGNATURES = {
     "tk_gemm_skinny": [P, L, P, L, P, P, L, I, I, I, I, I, F, P, L, P],
     "tk_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P, P],
     "tk_scale_rows": [P, L, F, I, P],
-    "tk_logit_options": [P, L, I, I, F, P, I, P],
+    "tk_logit_options": [P, L, I, I, F, F, P, I, P],
     "tk_gemm_tc_status": [],
     "tk_sample_status": [],
     "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, I, P],
@@ -90,7 +90,7 @@ _SIGNATURES = {
     "tk_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
     "tk_relu2": [P, L, I, P],
     "tk_scale_rows_f32": [P, L, P, F, I, I, I, P],
-    "tk_seq_conv": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, P, L, P, L, I, I, I, I, I, P, P, I, I, I, I, I, I, P],
+    "tk_seq_conv": [P, L, I, P, P, P, P, P, P, P, P, P, P, I, P, L, P, L, I, I, I, I, I, I, P, P, I, I, I, I, I, I, P],
     "tk_attn_pointwise_rows": [],
     "tk_attn_pointwise": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, F, I, P, P, P, I, P],
     "tk_attn_pointwise_mma_supported": [I, I, I, I, I],
@@ -99,6 +99,12 @@ _SIGNATURES = {
     "tk_rglru_scan": [P, I, P, P, P, P, L, P, L, P, P, P, P, I, P, I, I, I, P],
     "tk_mlstm_scan": [P, L, I, I, I, P, L, F, F, P, P, P, P, P, I, I, P, P, I, I, I, I, P],
     "tk_mlstm_norm_gate": [P, P, P, P, P, L, P, P, P, P, I, I, I, F, I, P],
+    "tk_ssd_max_state": [],
+    "tk_ssd_scan": [P, L, P, L, P, P, P, P, P, P, P, I, P, I, I, I, I, I, P],
+    "tk_gated_group_norm": [P, P, L, P, F, P, I, I, I, I, P],
+    "tk_qkv_maps_write": [P, L, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, P],
+    "tk_diff_combine": [P, P, I, I, F, F, F, I, P],
+    "tk_stream32_group_norm": [P, P, L, P, L, P, F, P, P, I, I, I, I, P],
 }
 
 
@@ -150,7 +156,7 @@ _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled"
             "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status",
             "tk_attn_latent_rows", "tk_attn_latent_max_rank", "tk_gemm_grouped_tile", "tk_attn_latent_mma_rows",
             "tk_attn_latent_mma_supported", "tk_attn_pointwise_rows", "tk_attn_pointwise_mma_supported",
-            "tk_attn_pointwise_mma_tokens"}
+            "tk_attn_pointwise_mma_tokens", "tk_ssd_max_state"}
 
 
 _fns: dict = {}

@@ -2,7 +2,7 @@
 arrangements; ``build_model`` turns a ``ModelSpec`` and its tensors into a runnable ``Stack``."""
 
 from tokenomos_b200.parts import (attention, block, convpos, embedding, ffn, hyper, latent, moe, norm,  # noqa: F401
-                                  parallel, recurrent, rope, shortconv)                                                     # (register)
+                                  parallel, plainpos, recurrent, rope, shortconv, ssd)                                                     # (register)
 from tokenomos_b200.parts.build import build_model
 from tokenomos_b200.parts.registry import Runtime, register
 

@@ -16,7 +16,9 @@ per output element, not per head); ``exact`` (the softmax's weights stay 32-bit 
 the values in kernels that do not need them in 16 bits); ``pointwise`` (no softmax: every visible
 key has the weight ``sigmoid(s + bias[h])`` of its own score, with an optional cap ``c tanh(s / c)``,
 a bias by distance ``- r1[h] ln(1 + r2[h] (i - j))`` and a query temperature ``1 + coef ln(floor((i + 1)
-/ every) + 1)``; ``PointwiseWeights``). A position part may keep state per request (a short
+/ every) + 1)``; ``PointwiseWeights``); ``diff`` (differential attention, ``DiffMaps``: every head has two
+softmax maps over the same values, each with its own half of the query and of the key, joined as
+``a_1 - lambda a_2`` and brought to unit root mean square per head). A position part may keep state per request (a short
 convolution on q, k and v): it then has ``state_specs()`` and is called with the layer's ``call``.
 """
 
@@ -46,6 +48,22 @@ class PointwiseWeights:
     head_bias: torch.Tensor | None = None
 
 
+@dataclass(frozen=True)
+class DiffMaps:
+    """Differential attention. A query head and a key head are two parts of ``head_dim / 2`` columns, one
+    per map; map m's scores read part m of both, and both maps weigh the same values. Per head ``o = a_1 -
+    lam a_2``, then ``o / sqrt(mean(o^2) + eps) * coef`` over the head's values (no weight).
+
+    To the attention kernels a map is a query head of the key's full width with zeros outside its part
+    (``parts.plainpos.PlainQKV`` with ``maps=2`` writes them so), which makes ``q . k`` the map's own
+    score against key heads that are stored once: the mixer then runs ``2 heads`` query heads over the
+    paged cache like any other, and one small kernel joins the pairs."""
+
+    lam: float
+    coef: float
+    eps: float
+
+
 class Attention:
     def __init__(self, qkv: Linear, o: Linear, heads: int, kv_heads: int, head_dim: int, rope,
                  eps: float, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
@@ -53,11 +71,20 @@ class Attention:
                  gate: Linear | None = None, kv_source: int | None = None,
                  gate_fused: bool = False, tuning: Tuning = DEFAULT_TUNING, sink: bool = False,
                  keep_first: int = 0, v_dim: int | None = None, v_is_k: bool = False,
-                 gate_kind: str = "head", exact: bool = False, pointwise: PointwiseWeights | None = None):
+                 gate_kind: str = "head", exact: bool = False, pointwise: PointwiseWeights | None = None,
+                 diff: DiffMaps | None = None):
         """``gate``: the per-head gate's projection as a part of its own; ``gate_fused``: its rows
         are the last of ``qkv``'s instead (after q, k, v, then zero rows up to a multiple of 8), so
-        that one product yields both."""
+        that one product yields both. With ``diff``, ``heads`` counts the maps (twice the output heads)
+        and ``head_dim`` is the key's full width (both parts)."""
         v_dim = head_dim if v_dim is None else int(v_dim)
+        self.diff = diff
+        # query heads as the projection holds them: a head's maps lie side by side in one head of it
+        self.maps = 2 if diff is not None else 1
+        if diff is not None and (heads % 2 or head_dim % 2 or pointwise is not None or sink or keep_first or v_is_k
+                                 or gate is not None or gate_fused):
+            raise ValueError("differential attention: an even count of maps over two-part keys, softmax weights "
+                             "without a sink or kept positions, values of their own, no gate")
         if v_is_k and (v_dim != head_dim or kv_source is not None):
             raise ValueError("attention: values that are the keys have the keys' size and a cache of their own")
         if gate_kind not in ("head", "element"):
@@ -73,7 +100,7 @@ class Attention:
         # (the tensor-core kernels take all of it but a value size of its own; the general
         # kernel takes everything)
         self.extended = bool(self.sink or self.keep_first or self.v_is_k or v_dim != head_dim
-                             or gate_kind != "head" or self.exact or pointwise is not None)
+                             or gate_kind != "head" or self.exact or pointwise is not None or diff is not None)
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads over {kv_heads} KV heads")
         if head_dim > ops.ATTENTION_MAX_HEAD_DIM:
@@ -95,7 +122,7 @@ class Attention:
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
         self.kv_source = kv_source
         own_kv = 0 if kv_source is not None else kv_heads
-        self.qkv_width = (heads + own_kv) * head_dim + (0 if v_is_k else own_kv * v_dim)
+        self.qkv_width = (heads // self.maps + own_kv) * head_dim + (0 if v_is_k else own_kv * v_dim)
         self.gate_fused = gate_fused
         self.gate_width = heads if gate_kind == "head" else heads * v_dim
         if gate_fused and gate is not None:
@@ -122,7 +149,9 @@ class Attention:
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T = x.shape[0]
         out = self._heads(self.qkv(x), x, ctx, call)
-        return self.o(out.view(T, self.heads * self.v_dim))
+        if self.diff is not None:
+            out = ops.diff_combine(out, self.diff.lam, self.diff.coef, self.diff.eps)
+        return self.o(out.view(T, (self.heads // self.maps) * self.v_dim))
 
     def _heads(self, proj: torch.Tensor, x: torch.Tensor | None, ctx: StepContext, call: int) -> torch.Tensor:
         """From the fused projection's rows to the gated heads' outputs [T, H, D]."""
@@ -372,6 +401,18 @@ def _pointwise(params: dict | None, tensors: dict) -> PointwiseWeights | None:
                             int(params.get("temp_every") or 0), vec("dist_r1"), vec("dist_r2"), vec("head_bias"))
 
 
+def _diff(params: dict | None, tensors: dict) -> DiffMaps | None:
+    """``params``: ``init`` (the constant of lambda), ``eps``; tensors ``lq1``, ``lk1``, ``lq2``, ``lk2`` (float32
+    [head_dim / 2]): ``lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + init``, one number for the layer, formed once
+    in 64-bit; the heads' outputs are scaled by ``1 - init``."""
+    if params is None:
+        return None
+    d = [tensors[n].double().reshape(-1) for n in ("lq1", "lk1", "lq2", "lk2")]
+    init = float(params["init"])
+    lam = float(torch.exp((d[0] * d[1]).sum()) - torch.exp((d[2] * d[3]).sum())) + init
+    return DiffMaps(lam, 1.0 - init, float(params["eps"]))
+
+
 @register("mixer", "attention")
 def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
     rope_spec = params["position"]
@@ -405,4 +446,4 @@ def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
         gate_fused=gated, tuning=rt.tuning, sink=params.get("sink", False),
         keep_first=params.get("keep_first", 0), v_dim=params.get("v_dim"), v_is_k=v_is_k,
         gate_kind=params.get("gate_kind", "head"), exact=params.get("exact", False),
-        pointwise=_pointwise(params.get("pointwise"), tensors))
+        pointwise=_pointwise(params.get("pointwise"), tensors), diff=_diff(params.get("diff"), tensors))

@@ -16,6 +16,7 @@ import torch
 from tokenomos_b200 import ops
 from tokenomos_b200.parts.contract import EMBED_CALL, SharedState, StateKey, StateSpec, StepContext
 from tokenomos_b200.parts.linear import Linear
+from tokenomos_b200.parts.norm import GatedRows
 from tokenomos_b200.parts.registry import DEFAULT_TUNING, Tuning, register
 from tokenomos_b200.parts.spec import LayerCall
 
@@ -88,11 +89,51 @@ def build_prenorm(parts: dict) -> PreNormBlock:
                         parts.get("post_ffn_norm"))
 
 
+class GatedResidualBlock:
+    """A pre-norm block whose sublayers join the stream through a gate computed from what they read:
+
+        h = norm1(x);  x <- x + sigmoid(R1 h + r1) * mixer(h);  h = norm2(x);  x <- x + sigmoid(R2 h + r2) * ffn(h)
+
+    on a 32-bit stream (the norms are ``rmsnorm32``, in groups or not). Like the other arrangements it
+    leaves each add to the next norm's kernel: a sublayer's output travels with its gate's rows
+    (``GatedRows``), and the kernel that reads the stream next forms ``x + y * sigmoid(g)`` in 32-bit.
+    A block may have no feed-forward."""
+
+    def __init__(self, mixer, ffn, pre_mixer, pre_ffn, gate_mixer: Linear, gate_ffn: Linear | None):
+        if getattr(pre_mixer, "stream_dtype", None) != torch.float32:
+            raise ValueError("a gated-residual block keeps its stream in 32-bit: its norms are rmsnorm32")
+        if (ffn is None) != (pre_ffn is None) or (ffn is None) != (gate_ffn is None):
+            raise ValueError("a gated-residual block's feed-forward comes with its norm and its gate")
+        self.mixer, self.ffn, self.pre_mixer, self.pre_ffn = mixer, ffn, pre_mixer, pre_ffn
+        self.gate_mixer, self.gate_ffn = gate_mixer, gate_ffn
+        self.capture_safe = all(getattr(p, "capture_safe", False) for p in (mixer, ffn, pre_mixer, pre_ffn)
+                                if p is not None)
+
+    def forward(self, h, residual, pending, ctx: StepContext, call: int):
+        if h is None:
+            h, residual = residual, None
+        x, stream = self.pre_mixer.add_norm(h, residual, pending)
+        gate = self.gate_mixer(x)
+        y = self.mixer.forward(x, ctx, call)
+        if self.ffn is None:
+            return y, stream, GatedRows(gate)
+        x, stream = self.pre_ffn.add_norm(y, stream, GatedRows(gate))
+        gate = self.gate_ffn(x)
+        return self.ffn.forward(x), stream, GatedRows(gate)
+
+
+@register("block", "prenorm_gated")
+def build_gated_residual(parts: dict) -> GatedResidualBlock:
+    return GatedResidualBlock(parts["mixer"], parts.get("ffn"), parts["pre_mixer_norm"], parts.get("pre_ffn_norm"),
+                              parts["mixer_gate"], parts.get("ffn_gate"))
+
+
 class Stack:
     def __init__(self, embedding: torch.Tensor, blocks: list, order: list[LayerCall], final_norm,
                  head: Linear | None, tuning: Tuning = DEFAULT_TUNING, embed_scale: float | None = None,
                  logit_softcap: float | None = None, suppress: tuple[int, ...] = (),
-                 extras: dict[str, torch.Tensor] | None = None, embedder=None, embed_wide: bool = False):
+                 extras: dict[str, torch.Tensor] | None = None, embedder=None, embed_wide: bool = False,
+                 logit_scale: float | None = None):
         self.embedding = embedding
         # the scaled embedding rows start a 32-bit stream unrounded (else they are rounded to the
         # storage type, as a 16-bit stream would hold them)
@@ -101,6 +142,7 @@ class Stack:
         self.extras = {name: t.float().contiguous() for name, t in (extras or {}).items()}
         self.embed_scale = None if embed_scale is None else float(embed_scale)
         self.logit_softcap = None if logit_softcap is None else float(logit_softcap)
+        self.logit_scale = None if logit_scale is None else float(logit_scale)
         if self.logit_softcap is not None and self.logit_softcap <= 0:
             raise ValueError(f"a logit soft cap of {logit_softcap}: it must be positive")
         bad = [t for t in suppress if not 0 <= int(t) < embedding.shape[0]]
@@ -220,6 +262,6 @@ class Stack:
                 pending = pending.gather(rows)
         y, _ = self.final_norm.add_norm(h, residual, pending)
         out = self.head(y, out_dtype=torch.float32)
-        if self.logit_softcap is not None or self.suppress is not None:
-            ops.logit_options(out, self.logit_softcap, self.suppress)
+        if self.logit_softcap is not None or self.suppress is not None or self.logit_scale is not None:
+            ops.logit_options(out, self.logit_softcap, self.suppress, self.logit_scale)
         return out

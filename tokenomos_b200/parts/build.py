@@ -16,6 +16,8 @@ SLOT_FAMILY = {
     "pre_ffn_norm": "norm",
     "post_mixer_norm": "norm",
     "post_ffn_norm": "norm",
+    "mixer_gate": "projection",
+    "ffn_gate": "projection",
 }
 
 
@@ -47,4 +49,4 @@ def build_model(spec: ModelSpec, tensors: dict, rt: Runtime) -> Stack:
     return Stack(tensors[spec.embedding.name], blocks, list(spec.order), final_norm, head,
                  tuning=rt.tuning, embed_scale=spec.embed_scale, logit_softcap=spec.logit_softcap,
                  suppress=spec.suppress, extras=extras, embedder=embedder,
-                 embed_wide=spec.embed_wide)
+                 embed_wide=spec.embed_wide, logit_scale=spec.logit_scale)

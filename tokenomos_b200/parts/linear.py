@@ -20,7 +20,7 @@ import torch
 import torch.nn.functional as F
 
 from tokenomos_b200 import ops
-from tokenomos_b200.parts.registry import DEFAULT_TUNING, Tuning
+from tokenomos_b200.parts.registry import DEFAULT_TUNING, Runtime, Tuning, register
 
 
 class Linear:
@@ -114,3 +114,10 @@ class Linear:
         if k >= t.tc_deep_k and t.skinny_rows < m <= t.tc_deep_rows and ops.gemm_tc_ok(x, self.weight):
             return "tc"
         return "library"
+
+
+@register("projection", "linear")
+def build_linear(params: dict, tensors: dict, rt: Runtime) -> Linear:
+    """A projection as a part of a block arrangement's own (family ``projection``): tensors ``weight`` and,
+    optionally, ``bias``."""
+    return Linear(tensors["weight"], tensors.get("bias"), rt.tuning)

@@ -28,12 +28,16 @@ class RoutedExperts:
 
     def __init__(self, router: Linear, up: torch.Tensor, down: torch.Tensor, top: int, scale: float,
                  shared_up: Linear | None = None, shared_down: Linear | None = None, shared_gate: bool = False,
-                 library_rows: int = 1024, activation: str = "relu2"):
+                 library_rows: int = 1024, activation: str = "relu2", shared: object | None = None):
         """``up`` [E, ff, width], ``down`` [E, width, ff]; ``router`` [E (+ 1 if ``shared_gate``) (+ zero
         rows), width] (it may carry a bias). ``activation`` "relu2": ``act(v) = relu(v)^2``; "swiglu": an
         expert is ``W_down (silu(W_gate h) * (W_up h))`` and ``up`` holds each expert's gate rows, then its
         up rows ([E, 2 ff, width]; kept with gate and up alternating in runs of 8 where the kernels
-        take that)."""
+        take that). ``shared``: a whole feed-forward part that every token runs and whose output is added (in
+        place of ``shared_up`` / ``shared_down``, which are the ``relu2`` form)."""
+        self.shared = shared
+        if shared is not None and (shared_up is not None or shared_gate):
+            raise ValueError("mixture of experts: one shared expert")
         if activation not in ("relu2", "swiglu"):
             raise ValueError(f"mixture of experts: activation {activation!r}: 'relu2' or 'swiglu'")
         self.activation = activation
@@ -86,6 +90,8 @@ class RoutedExperts:
         return ops.moe_combine(y, pair_row, w, self._shared(x), gate)
 
     def _shared(self, x: torch.Tensor) -> torch.Tensor | None:
+        if self.shared is not None:
+            return self.shared.forward(x)
         if self.shared_up is None:
             return None
         return self.shared_down(ops.relu2(self.shared_up(x)))
@@ -126,8 +132,13 @@ def build_routed_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExpe
 def build_gated_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExperts:
     """Experts ``W_down (silu(W_gate h) * (W_up h))``; router logits ``W_r h + b`` in 32-bit; the weights
     of the ``top`` experts with the largest logits are the softmax over those logits alone (which is the
-    softmax over all of them, renormalised over the chosen)."""
+    softmax over all of them, renormalised over the chosen). Tensors ``shared.gate|up|down``: a shared expert
+    of the same form that every token runs, added unweighted."""
     n = params["experts"]
+    shared = None
+    if "shared.gate" in tensors:
+        from tokenomos_b200.parts.ffn import build_swiglu
+        shared = build_swiglu({}, {k: tensors["shared." + k] for k in ("gate", "up", "down")}, rt)
     up = torch.stack([torch.cat((tensors[f"e{i}.gate"], tensors[f"e{i}.up"])) for i in range(n)])
     down = torch.stack([tensors[f"e{i}.down"] for i in range(n)])
     w = tensors["router"].to(rt.dtype)
@@ -138,4 +149,4 @@ def build_gated_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExper
         if bias is not None:
             bias = torch.cat((bias.float(), torch.zeros(pad, dtype=torch.float32, device=bias.device)))
     return RoutedExperts(Linear(w, bias, tuning=rt.tuning), up, down, params["top"], params.get("scale", 1.0),
-                         library_rows=rt.tuning.grouped_library_rows, activation="swiglu")
+                         library_rows=rt.tuning.grouped_library_rows, activation="swiglu", shared=shared)

@@ -117,6 +117,7 @@ FEED_FORWARDS: dict[str, Builder] = {}
 NORMS: dict[str, Builder] = {}
 POSITIONS: dict[str, Builder] = {}
 EMBEDDINGS: dict[str, Builder] = {}
+PROJECTIONS: dict[str, Builder] = {}
 BLOCKS: dict[str, Callable] = {}
 
 _FAMILIES = {
@@ -125,6 +126,7 @@ _FAMILIES = {
     "norm": NORMS,
     "position": POSITIONS,
     "embedding": EMBEDDINGS,
+    "projection": PROJECTIONS,
     "block": BLOCKS,
 }
 

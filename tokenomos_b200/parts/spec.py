@@ -97,6 +97,8 @@ class ModelSpec:
     # the scaled rows are kept in 32-bit (they start a 32-bit residual stream unrounded)
     embed_wide: bool = False
     logit_softcap: float | None = None
+    # the logits times a constant, before the cap
+    logit_scale: float | None = None
     suppress: tuple[int, ...] = ()
     # tensors of the stack itself (not of a block), by the name ``StreamAdd.tensor`` uses
     extras: tuple[tuple[str, TensorDecl], ...] = ()
