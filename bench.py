@@ -1521,6 +1521,258 @@ def lisorax_kernels(z: dict, pk: dict) -> list[dict]:
         "Laposun: up with relu^2 in the epilogue, down")
     return rows
 
+# ---------------------------------------------------------------------------------------------
+# --design fakelorn: the Fakelorn decoder beside Laposun (the other design with latent attention, a
+# 32-bit stream, dense and expert feed-forwards with a shared expert) at equal sizes
+# ---------------------------------------------------------------------------------------------
+FAKELORN_SIZES = {
+    # the Laposun side reads its own keys; Fakelorn reads width, heads, dim, rot_dim, q_rank, kv_rank, ff, experts,
+    # top, expert_ff, shared_ff, window, layers, vocab and the differential and state-space mixers' sizes
+    "w2048": dict(LAPOSUN_SIZES["w2048"], diff_heads=16, diff_kv=4, diff_dim=64, diff_vdim=128, ssm_heads=64, ssm_vdim=64,
+                  ssm_state=128, ssm_groups=8, norm_groups=4),
+    "w1024": dict(LAPOSUN_SIZES["w1024"], diff_heads=16, diff_kv=4, diff_dim=32, diff_vdim=64, ssm_heads=32, ssm_vdim=64,
+                  ssm_state=128, ssm_groups=4, norm_groups=4),
+}
+
+
+def fakelorn_config(z: dict) -> dict:
+    """Groups of four layers: latent attention (dense feed-forward), state-space (experts + shared),
+    differential attention with a window (dense), latent attention that reads the first one's cache (experts)."""
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    layers = []
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 1:
+            layer = {"type": "mamba2", "mixer": {"heads": z["ssm_heads"], "vdim": z["ssm_vdim"], "state": z["ssm_state"],
+                                                 "groups": z["ssm_groups"], "conv": z["taps"], "norm_groups": z["ssm_groups"]}}
+        elif kind == 2:
+            layer = {"type": "attention", "mixer": {"heads": z["diff_heads"], "kv_heads": z["diff_kv"], "dim": z["diff_dim"],
+                                                    "vdim": z["diff_vdim"], "scale": z["diff_dim"] ** -0.5, "diff": 0.5,
+                                                    "mask": {"size": z["window"]}}}
+        else:
+            mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["dim"], "q_rank": z["q_rank"],
+                     "kv_rank": z["kv_rank"], "scale": (z["dim"] + z["rot_dim"]) ** -0.5,
+                     "rot": {"base": 1000000.0, "dims": z["rot_dim"]}}
+            if kind == 3:
+                mixer["kv_from"] = i - 3
+            layer = {"type": "latent_attention", "mixer": mixer}
+        layers.append(dict(layer, mlp=dense if kind % 2 == 0 else moe))
+    return {"architecture": "Fakelorn", "vocab": z["vocab"], "width": z["width"],
+            "norm": {"eps": 1e-6, "groups": z["norm_groups"]}, "logit_scale": 0.5, "logit_softcap": 30.0, "layers": layers}
+
+
+def fakelorn_prefill_flops(z: dict, tokens: int) -> float:
+    """Multiply-adds times two of one prompt of ``tokens`` tokens: the latent layers as this engine computes them
+    (scores and values in the latent's space), the differential layers as the design defines them (two maps of
+    ``dim`` columns over values of ``vdim``), the state-space layers as their recurrence (an update and a read of
+    [state, vdim] per token and head)."""
+    W, H, D, Dr, R, Rq = z["width"], z["heads"], z["dim"], z["rot_dim"], z["kv_rank"], z["q_rank"]
+    Hd, Gd, Dd, Vd = z["diff_heads"], z["diff_kv"], z["diff_dim"], z["diff_vdim"]
+    Hs, Vs, N, Gs = z["ssm_heads"], z["ssm_vdim"], z["ssm_state"], z["ssm_groups"]
+    pairs = tokens * (tokens + 1) / 2
+    windowed = sum(min(i + 1, z["window"]) for i in range(tokens))
+    dense = 3 * W * z["ff"]
+    moe = 3 * W * (z["top"] * z["expert_ff"] + z["shared_ff"]) + W * z["experts"]
+    flops = 0.0
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 1:
+            inner = Hs * Vs
+            per_tok = W * (2 * inner + 2 * Gs * N + Hs) + inner * W + 2 * Hs * N * Vs
+        elif kind == 2:
+            per_tok = W * (Hd * 2 * Dd + Gd * 2 * Dd + Gd * Vd) + Hd * Vd * W
+            flops += 2.0 * windowed * Hd * 2 * (Dd + Vd)
+        else:
+            per_tok = W * (Rq + (R + Dr if kind == 0 else 0) + H * D) + Rq * H * (D + Dr) + 2 * H * D * R + H * D * W
+            flops += 2.0 * pairs * H * (2 * R + Dr)
+        flops += 2.0 * tokens * (per_tok + W * W * 2 + (dense if kind % 2 == 0 else moe))
+    return flops + 2.0 * z["vocab"] * W
+
+
+def fakelorn_kernels(z: dict, pk: dict) -> list[dict]:
+    """Each kernel the Fakelorn path adds beside the kernel of an earlier model that does the like work, on the
+    shapes of a 2,048-token prompt portion of one sequence (or 64 decoded tokens behind 2,048 positions), L2
+    flushed before every launch, CUDA events around the launches, median of 20. ``frac``: bytes over time
+    against the measured copy bandwidth, or flops over time against the measured bf16 rate. (The latent
+    attention's kernels, the experts' and the dense feed-forward's are Laposun's and Lisorax's own.)"""
+    import torch
+
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.rope import Rotary
+
+    bf, dev = torch.bfloat16, "cuda"
+    T, W, P = 2048, z["width"], 16
+    H, G, D, V = z["diff_heads"], z["diff_kv"], z["diff_dim"], z["diff_vdim"]
+    Hs, Vs, N, Gs, taps = z["ssm_heads"], z["ssm_vdim"], z["ssm_state"], z["ssm_groups"], z["taps"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def add(name, ours_us, theirs_us, ours_work, theirs_work, unit, like):
+        peak = pk["hbm_gbs"] * 1e3 if unit == "bytes" else pk["bf16_tflops"] * 1e6       # per microsecond
+        fo = ours_work / ours_us / peak
+        row = {"kernel": name, "like": like, "unit": unit, "fakelorn_us": round(ours_us, 1), "fakelorn_frac": round(fo, 4)}
+        if theirs_us is not None:
+            ft = theirs_work / theirs_us / peak
+            row.update(like_us=round(theirs_us, 1), like_frac=round(ft, 4), times_further_from_roofline=round(ft / fo, 2))
+        rows.append(row)
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    cu, zero1, one1 = i32([0, T]), i32([0]), i32([1])
+
+    def tiles_of(size):
+        k = T // size
+        return (torch.zeros(k, dtype=torch.int32, device=dev), torch.arange(0, T, size, dtype=torch.int32, device=dev),
+                torch.arange(0, T, size, dtype=torch.int32, device=dev), torch.full((k,), size, dtype=torch.int32, device=dev))
+
+    # 1. the stream: gated add + norm in groups, beside Darizen's add + norm
+    nw = torch.ones(W, device=dev)
+    res32 = torch.randn(T, W, device=dev)
+    y, gate = torch.randn(T, W, device=dev).to(bf), torch.randn(T, W, device=dev).to(bf)
+    add("gated residual add + norm in groups",
+        _timed_us(lambda: ops.stream32_group_norm(res32, y, gate, nw, 1e-6, z["norm_groups"], bf), flush),
+        _timed_us(lambda: ops.stream32_add_norm(res32, y, nw, 1e-6), flush),
+        T * W * (4 + 2 + 2 + 4 + 2), T * W * (4 + 2 + 4 + 2), "bytes", "Darizen: residual add + norm")
+
+    # 2. differential attention: queries as maps + cache write, beside Darizen's rotation + cache write
+    pages = T // P + 1
+    Dk = 2 * D
+    pool = torch.zeros(pages, 2, G, P, max(Dk, V), dtype=bf, device=dev)
+    tbl = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1)
+    qkv = torch.randn(T, H * Dk + G * Dk + G * V, device=dev).to(bf)
+    rot = Rotary(Dk, Dk, 1e6, "half", None, dev)
+    qkv_like = torch.randn(T, (H + 2 * G) * Dk, device=dev).to(bf)
+    pool_like = torch.zeros(pages, 2, G, P, Dk, dtype=bf, device=dev)
+    add("differential attention: queries as maps + cache write",
+        _timed_us(lambda: ops.qkv_maps_write(qkv, pos, seq, tbl, pool, H, G, D, V, 2), flush),
+        _timed_us(lambda: ops.rotary_write(qkv_like, pool_like, rot.freq, 1.0, pos, seq, tbl, H, G, Dk, Dk, P, False, False), flush),
+        T * ((H * Dk + G * Dk + G * V) * 2 + 2 * H * Dk * 2 + G * (Dk + V) * 2), T * (H + 2 * G) * Dk * 4, "bytes",
+        "Darizen: rotation + cache write")
+
+    # 3. prompt attention: 2 H maps as heads of the key's width over the window + the join of the pairs,
+    # beside softmax attention with H heads of the same key and value sizes
+    win = z["window"]
+    windowed = sum(min(i + 1, win) for i in range(T))
+    q = ops.qkv_maps_write(qkv, pos, seq, tbl, pool, H, G, D, V, 2)
+    if V == Dk and ops.attention_mma_supported(2 * H, G, Dk, bf):
+        tc = ops.attention_prefill_tc_supported(2 * H, G, Dk, bf)
+        per = (ops.attention_prefill_tc_tokens if tc else ops.attention_prefill_mma_tokens)(2 * H, G)
+        t0 = torch.arange(0, T, per, dtype=torch.int32, device=dev)
+        nt = torch.full_like(t0, per)
+        out = torch.empty_like(q)
+        q1 = torch.randn(T, H, Dk, device=dev).to(bf)
+        out1 = torch.empty_like(q1)
+        tc1 = ops.attention_prefill_tc_supported(H, G, Dk, bf)
+        per1 = (ops.attention_prefill_tc_tokens if tc1 else ops.attention_prefill_mma_tokens)(H, G)
+        t01 = torch.arange(0, T, per1, dtype=torch.int32, device=dev)
+        nt1 = torch.full_like(t01, per1)
+
+        def ours():
+            if tc:
+                ops.attention_prefill_tc(q, pool, out, pos, seq, tbl, t0, nt, win, D ** -0.5, None, 1)
+            else:
+                ops.attention_prefill_mma(q, pool, out, pos, seq, tbl, t0, nt, win, D ** -0.5)
+            return ops.diff_combine(out, 0.3, 0.5, 1e-6)
+
+        def like():
+            if tc1:
+                ops.attention_prefill_tc(q1, pool, out1, pos, seq, tbl, t01, nt1, win, D ** -0.5, None, 1)
+            else:
+                ops.attention_prefill_mma(q1, pool, out1, pos, seq, tbl, t01, nt1, win, D ** -0.5)
+
+        add("differential prompt attention (%s) + join" % ("tcgen05" if tc else "mma.sync"), _timed_us(ours, flush, reps=5),
+            _timed_us(like, flush, reps=5), 4.0 * windowed * H * (D + V), 2.0 * windowed * H * (Dk + V),
+            "flops", "Darizen: prompt attention, softmax, as many heads of the key's width")
+
+        # 4. decode attention: 64 sequences behind T positions + the join
+        Bd = 64
+        dpos = torch.full((Bd,), T - 1, dtype=torch.int32, device=dev)
+        dseq = torch.arange(Bd, dtype=torch.int32, device=dev)
+        dtbl = tbl.expand(Bd, -1).contiguous()
+        dq, dq1 = q[:Bd].contiguous(), q1[:Bd].contiguous()
+        dout, dout1 = torch.empty_like(dq), torch.empty_like(dq1)
+
+        def ours_decode():
+            ops.attention_decode_mma(dq, pool, dout, dpos, dseq, dtbl, None, win, D ** -0.5, 2)
+            return ops.diff_combine(dout, 0.3, 0.5, 1e-6)
+
+        add("differential decode attention, 64 tokens + join", _timed_us(ours_decode, flush),
+            _timed_us(lambda: ops.attention_decode_mma(dq1, pool, dout1, dpos, dseq, dtbl, None, win, D ** -0.5, 2), flush),
+            Bd * G * min(T, win) * (Dk + V) * 2, Bd * G * min(T, win) * (Dk + V) * 2, "bytes",
+            "Darizen: decode attention, softmax")
+
+    # 5. state-space mixer: convolution + activation, scan, gate + norm in groups
+    inner, bc = Hs * Vs, 2 * Gs * N
+    proj = torch.randn(T, 2 * inner + bc, device=dev).to(bf) * 0.5
+    ctaps = torch.randn(inner + bc, taps, device=dev) * 0.3
+    cbias = torch.zeros(inner + bc, device=dev)
+    cstate = torch.zeros(66, taps - 1, inner + bc, device=dev)
+    tl = tiles_of(ops.seq_conv_tile(16, T, inner + bc))
+    add("state-space: convolution + silu over x, B, C",
+        _timed_us(lambda: ops.seq_conv(proj[:, inner:], ctaps, cbias, cstate, cu, zero1, one1, tl, bf, act=True), flush), None,
+        T * (inner + bc) * 4, 0, "bytes", "Lisorax: the same kernel without the activation")
+    xbc = ops.seq_conv(proj[:, inner:], ctaps, cbias, cstate, cu, zero1, one1, tl, bf, act=True)
+    dt = torch.randn(T, Hs, device=dev)
+    dtb, alog, dsk = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
+    S = torch.zeros(66, Hs, N, Vs, device=dev)
+    cu64 = torch.arange(0, T + 1, T // 64, dtype=torch.int32, device=dev)
+    z64, o64 = torch.zeros(64, dtype=torch.int32, device=dev), torch.arange(1, 65, dtype=torch.int32, device=dev)
+    cu1 = torch.arange(0, 65, dtype=torch.int32, device=dev)
+    # the like: Lisorax's matrix memory (a [dim, vdim + 1] state per head walked token by token) at equal state size
+    Hm, Dm, Vm = Hs, N, Vs
+    mq = torch.randn(T, 2 * Hm * Dm + 2 * Hm * Vm, device=dev).to(bf) * 0.3
+    mg = torch.randn(T, 2 * Hm + (-2 * Hm % 8), device=dev)
+    mS = torch.zeros(66, Hm, Vm + 1, Dm, device=dev)
+    mm = torch.zeros(66, Hm, device=dev)
+    scan_flops = 2.0 * T * Hs * N * Vs * 2
+    mem_flops = 2.0 * T * Hm * Dm * (Vm + 1) * 2
+
+    def mem(cu_, ctx_, slot_, n, rows_=T):
+        return ops.mlstm_scan(mq[:rows_], (0, Hm * Dm, 2 * Hm * Dm), mg[:rows_], 15.0, Dm ** -0.5, mS, mm, cu_, ctx_, slot_, n,
+                              Hm, Dm, Vm)
+
+    add("state-space scan over 2,048 tokens of one sequence (32-bit, CUDA cores)",
+        _timed_us(lambda: ops.ssd_scan(xbc, dt, dtb, alog, dsk, S, cu, zero1, one1, 1, Hs, Vs, N, Gs), flush, reps=5),
+        _timed_us(lambda: mem(cu, zero1, one1, 1), flush, reps=5), scan_flops, mem_flops, "flops",
+        "Lisorax: matrix memory scan at equal state size (of the bf16 tensor rate; both are 32-bit)")
+    add("state-space scan over 2,048 tokens of 64 sequences",
+        _timed_us(lambda: ops.ssd_scan(xbc, dt, dtb, alog, dsk, S, cu64, z64, o64, 64, Hs, Vs, N, Gs), flush, reps=5),
+        _timed_us(lambda: mem(cu64, z64, o64, 64), flush, reps=5), scan_flops, mem_flops, "flops",
+        "Lisorax: matrix memory scan at equal state size")
+    add("state-space scan, one token of 64 sequences (state read and written)",
+        _timed_us(lambda: ops.ssd_scan(xbc[:64], dt[:64], dtb, alog, dsk, S, cu1, o64, o64, 64, Hs, Vs, N, Gs), flush),
+        _timed_us(lambda: mem(cu1, o64, o64, 64, 64), flush), 64 * Hs * N * Vs * 8, 64 * Hm * (Vm + 1) * Dm * 8, "bytes",
+        "Lisorax: matrix memory, one token of 64 sequences")
+    yv = ops.ssd_scan(xbc, dt, dtb, alog, dsk, S, cu, zero1, one1, 1, Hs, Vs, N, Gs)
+    gw = torch.ones(inner, device=dev)
+    num, m = mem(cu, zero1, one1, 1)
+    g0 = 2 * Hm * Dm + Hm * Vm
+    add("state-space: gate + norm in groups",
+        _timed_us(lambda: ops.gated_group_norm(yv, proj[:, :inner], gw, 1e-6, Gs), flush),
+        _timed_us(lambda: ops.mlstm_norm_gate(num, m, mm, gw, mq[:, g0:g0 + Hm * Vm], seq, cu, one1, 1e-6, bf), flush),
+        T * inner * (4 + 2 + 2), T * Hm * (Vm * (4 + 2 + 2) + 8), "bytes", "Lisorax: matrix memory division + head norm + gate")
+
+    # 6. latent attention's output gate per element, beside the gate per head in the product's epilogue
+    Hl, Dl, R = z["heads"], z["dim"], z["kv_rank"]
+    lat = torch.randn(Hl, T, R, device=dev).to(bf)
+    uv = torch.randn(Hl, Dl, R, device=dev).to(bf) * 0.05
+    ge = torch.randn(T, Hl * Dl, device=dev).to(bf)
+    gh = torch.randn(T, Hl, device=dev).to(bf)
+    o1 = torch.empty(T, Hl, Dl, dtype=bf, device=dev)
+
+    def gated_elements():
+        ops.gemm_batched(lat, uv, out=o1.transpose(0, 1))
+        return ops.sigmoid_gate(o1, ge)
+
+    add("latent attention: values' up-projection + gate per element (2 kernels)", _timed_us(gated_elements, flush),
+        _timed_us(lambda: ops.gemm_batched(lat, uv, out=o1.transpose(0, 1), gate=gh), flush),
+        2.0 * T * Hl * Dl * R, 2.0 * T * Hl * Dl * R, "flops", "Laposun: the same product with the gate per head in its epilogue")
+    return rows
+
+
 def run_design(name: str, args, warmup: int) -> int:
     """``--design darizen``: decode (batch 8 and 64) and prefill (2,048 tokens) throughput of
     Darizen stacks at a few real layer sizes, beside the LFM3 stack of sliding-window attention
@@ -1533,14 +1785,15 @@ def run_design(name: str, args, warmup: int) -> int:
     from tokenomos_b200.weights import write_model_folder
 
     pk = peaks()
-    sizes = {"laposun": LAPOSUN_SIZES, "lisorax": LISORAX_SIZES}.get(name, DESIGN_SIZES)
+    sizes = {"laposun": LAPOSUN_SIZES, "lisorax": LISORAX_SIZES, "fakelorn": FAKELORN_SIZES}.get(name, DESIGN_SIZES)
     for size, z in sizes.items():
         if getattr(args, "design_size", None) and size != args.design_size:
             continue
         line = {"design": name, "size": size, "sizes": z, "dtype": "bf16",
                 "data": "synthetic token ids, random-init weights N(0, 0.02)"}
         arms = {"laposun": (("laposun", laposun_config(z)), ("darizen", darizen_config(z))),
-                "lisorax": (("lisorax", lisorax_config(z)), ("laposun", laposun_config(z)))}.get(
+                "lisorax": (("lisorax", lisorax_config(z)), ("laposun", laposun_config(z))),
+                "fakelorn": (("fakelorn", fakelorn_config(z)), ("laposun", laposun_config(z)))}.get(
                     name, (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z))))
         for arm, config in arms:
             with tempfile.TemporaryDirectory(prefix="tokenomos_b200_design_") as tmp:
@@ -1563,14 +1816,15 @@ def run_design(name: str, args, warmup: int) -> int:
                 res[f"decode_b{batch}"] = {"tok_s": round(d["tok_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
                                            "launches": d["launches_per_step"]}
             pf = device_prefill(model, cfg, args.page)
-            flops = {"laposun": laposun_prefill_flops, "lisorax": lisorax_prefill_flops}.get(
+            flops = {"laposun": laposun_prefill_flops, "lisorax": lisorax_prefill_flops, "fakelorn": fakelorn_prefill_flops}.get(
                 arm, lambda *_: pf["flops"])(z, pf["tokens"])
             res["prefill_2048"] = {"tok_s": round(pf["tok_s"], 1), "ms": round(pf["ms"], 3),
                                    "frac": round(flops / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
             line[arm] = res
             del model
             torch.cuda.empty_cache()
-        line["kernels"] = {"laposun": laposun_kernels, "lisorax": lisorax_kernels}.get(name, design_kernels)(z, pk)
+        line["kernels"] = {"laposun": laposun_kernels, "lisorax": lisorax_kernels, "fakelorn": fakelorn_kernels}.get(
+            name, design_kernels)(z, pk)
         print(json.dumps(line), flush=True)
     return 0
 
@@ -1599,9 +1853,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--trace", default=None,
                     help="--workload: write one JSON record per step of an extra pass to this file")
-    ap.add_argument("--design", default=None, choices=["darizen", "laposun", "lisorax"],
+    ap.add_argument("--design", default=None, choices=["darizen", "laposun", "lisorax", "fakelorn"],
                     help="the named design beside the closest existing model at equal sizes instead (darizen beside "
-                         "LFM3, laposun beside darizen, lisorax beside laposun)")
+                         "LFM3, laposun beside darizen, lisorax beside laposun, fakelorn beside laposun)")
     ap.add_argument("--design-size", default=None, help="only this size of the design's table")
     ap.add_argument("--sweep", action="store_true",
                     help="decode and prefill at other batch sizes and context lengths instead")
