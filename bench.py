@@ -396,6 +396,7 @@ def kernel_case(name: str) -> None:
     ``gemm_tc64``: the tcgen05 product of 64 rows with a [6144, 2048] matrix, 16 launches;
     ``conv_tile``: the tiled gated short conv over a 2,048-token portion of 2,048 channels (width 3,
     tiles of 16 tokens), 20 launches in a CUDA graph that is replayed five times;
+    ``ssd_scan``: the state-space scan over a 2,048-token portion of one sequence, 4 launches;
     ``attn_portions`` (a measurement, not a profiler case): the tcgen05 prefill attention on
     portions behind cached contexts, with a tile's keys shared by 1 to 16 CTAs."""
     import torch
@@ -439,6 +440,18 @@ def kernel_case(name: str) -> None:
             print(line, flush=True)
         if ops.attention_prefill_tc_status():
             raise RuntimeError("the tcgen05 attention reported an error")
+    elif name == "ssd_scan":
+        # the state-space scan over a 2,048-token portion of one sequence (32 heads of 64 columns, a state
+        # of 128 rows, 4 groups), 4 launches
+        T, H, V, N, G = 2048, 32, 64, 128, 4
+        xbc = torch.randn(T, H * V + 2 * G * N, device=dev).to(bf16) * 0.5
+        dt = torch.randn(T, H, device=dev)
+        vec = [torch.zeros(H, device=dev), torch.zeros(H, device=dev), torch.ones(H, device=dev)]
+        S = torch.zeros(2, H, N, V, device=dev)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        for _ in range(4):
+            ops.ssd_scan(xbc, dt, *vec, S, i32([0, T]), i32([0]), i32([1]), 1, H, V, N, G)
+        torch.cuda.synchronize()
     elif name == "gemm_tc64":
         ws = [torch.randn(6144, 2048, device=dev, dtype=bf16) * 0.02 for _ in range(8)]
         x = torch.randn(64, 2048, device=dev, dtype=bf16)
@@ -1791,10 +1804,14 @@ def run_design(name: str, args, warmup: int) -> int:
             continue
         line = {"design": name, "size": size, "sizes": z, "dtype": "bf16",
                 "data": "synthetic token ids, random-init weights N(0, 0.02)"}
-        arms = {"laposun": (("laposun", laposun_config(z)), ("darizen", darizen_config(z))),
-                "lisorax": (("lisorax", lisorax_config(z)), ("laposun", laposun_config(z))),
-                "fakelorn": (("fakelorn", fakelorn_config(z)), ("laposun", laposun_config(z)))}.get(
-                    name, (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z))))
+        if name == "laposun":
+            arms = (("laposun", laposun_config(z)), ("darizen", darizen_config(z)))
+        elif name == "lisorax":
+            arms = (("lisorax", lisorax_config(z)), ("laposun", laposun_config(z)))
+        elif name == "fakelorn":
+            arms = (("fakelorn", fakelorn_config(z)), ("laposun", laposun_config(z)))
+        else:
+            arms = (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z)))
         for arm, config in arms:
             with tempfile.TemporaryDirectory(prefix="tokenomos_b200_design_") as tmp:
                 folder = Path(tmp) / arm
@@ -1840,7 +1857,7 @@ def main() -> int:
     ap.add_argument("--profile", default=None, choices=["decode", "decode_graph", "prefill", "ingraph"],
                     help="run only a small case for a profiler (see profile_case) and exit; ingraph: "
                          "the cost of each kind of kernel inside the captured decode step (ingraph_table)")
-    ap.add_argument("--kernel", default=None, choices=["gemm_tc64", "conv_tile", "attn_portions"],
+    ap.add_argument("--kernel", default=None, choices=["gemm_tc64", "conv_tile", "attn_portions", "ssd_scan"],
                     help="run only one kernel over rotating operands for a profiler (see kernel_case) and exit")
     ap.add_argument("--ctx", type=int, default=2048, help="--profile: positions already cached")
     ap.add_argument("--gpus", type=int, default=1)

@@ -48,6 +48,36 @@ qkv_maps_write_kernel(const T* qkv, int64_t stride, const int* positions, const 
     for (int i = threadIdx.x; i < G * V; i += blockDim.x) vd[(size_t)(i / V) * P * Dp + i % V] = v[i];
 }
 
+// The same, 16 bytes at a time: bfloat16 with D, V, the rows' distance and the cache row whole 16-byte
+// chunks, so that a chunk of the expanded query lies wholly inside or outside its map's part.
+__global__ void __launch_bounds__(128)
+qkv_maps_write_vec_kernel(const __nv_bfloat16* qkv, int64_t stride, const int* positions, const int* tok_seq,
+                          const int* block_table, int bt_stride, __nv_bfloat16* q_out, __nv_bfloat16* pool, int H, int G,
+                          int D, int V, int maps, int P, int Dp) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const uint4* row = reinterpret_cast<const uint4*>(qkv + (size_t)t * stride);
+    const int DK = maps * D, dk8 = DK / 8, d8 = D / 8, v8 = V / 8;
+    uint4* qo = reinterpret_cast<uint4*>(q_out + (size_t)t * H * maps * DK);
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < H * maps * dk8; i += blockDim.x) {
+        const int c = i % dk8, hm = i / dk8;
+        const int m = hm % maps;
+        qo[i] = c / d8 == m ? row[hm * d8 + (c - m * d8)] : zero;
+    }
+    if (pool == nullptr) return;
+    const int pos = positions[t];
+    const int page = TK_PAGE(TK_K_QKV_MAPS, block_table[(size_t)tok_seq[t] * bt_stride + pos / P]);
+    uint4* kd = reinterpret_cast<uint4*>(pool + (((size_t)page * 2 + 0) * G * P + pos % P) * Dp);
+    uint4* vd = reinterpret_cast<uint4*>(pool + (((size_t)page * 2 + 1) * G * P + pos % P) * Dp);
+    const uint4* k = row + (size_t)H * dk8;
+    const uint4* v = k + (size_t)G * dk8;
+    const size_t head = (size_t)P * Dp / 8;
+    for (int i = threadIdx.x; i < G * dk8; i += blockDim.x) kd[(size_t)(i / dk8) * head + i % dk8] = k[i];
+    for (int i = threadIdx.x; i < G * v8; i += blockDim.x) vd[(size_t)(i / v8) * head + i % v8] = v[i];
+}
+
 // qkv: [T, >= (H + G) maps D + G V] rows `stride` apart; q_out: [T, H maps, maps D]; pool (null: the layer
 // has no keys of its own): [pages, 2, G, P, Dp] with Dp >= max(maps D, V).
 TK_API int tk_qkv_maps_write(const void* qkv, int64_t stride, const int* positions, const int* tok_seq,
@@ -57,6 +87,13 @@ TK_API int tk_qkv_maps_write(const void* qkv, int64_t stride, const int* positio
     TK_CHECK_ARG(pool == nullptr || (block_table != nullptr && P > 0 && G > 0 && Dp >= maps * D && Dp >= V),
                  "qkv_maps_write: cache rows of %d for keys of %d and values of %d", Dp, maps * D, V);
     if (tokens == 0) return 0;
+    if (dtype == TK_BF16 && D % 8 == 0 && V % 8 == 0 && stride % 8 == 0 && (pool == nullptr || Dp % 8 == 0) &&
+        ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)pool & 15) == 0) {
+        tk_launch(qkv_maps_write_vec_kernel, dim3(tokens), dim3(128), 0, stream, (const __nv_bfloat16*)qkv, stride, positions,
+                  tok_seq, block_table, bt_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, H, G, D, V, maps, P, Dp);
+        TK_CHECK_LAUNCH("qkv_maps_write_vec");
+        return 0;
+    }
     if (dtype == TK_F32)
         tk_launch(qkv_maps_write_kernel<float>, dim3(tokens), dim3(128), 0, stream, (const float*)qkv, stride, positions,
                   tok_seq, block_table, bt_stride, (float*)q_out, (float*)pool, H, G, D, V, maps, P, Dp);

@@ -330,6 +330,14 @@ TK_API int tk_sigmoid_gate(void* x, const void* g, int64_t ldg, int rows, int wi
 // (ITEMS per lane: 4 elements at a time where VEC, which wants the group a multiple of 4 and every
 // row 16-byte aligned), else it reads its own writes back from stream_out.
 // ---------------------------------------------------------------------------------------------
+// sigmoid(g): 16-bit storage takes the special-function unit's exponential and reciprocal (a few ulp of a
+// float, far below the rounding of the gate itself), 32-bit storage the accurate functions
+template <typename T>
+__device__ __forceinline__ float gate_of(float g) {
+    if constexpr (sizeof(T) == 2) return rcp_approx(1.0f + ex2_approx(g * TK_NEG_LOG2E));
+    return 1.0f / (1.0f + expf(-g));
+}
+
 template <typename T, int ITEMS, bool VEC>
 __global__ void __launch_bounds__(128)
 stream32_group_norm_kernel(const float* stream_in, const T* x, int64_t x_stride, const T* gate, int64_t gate_stride,
@@ -361,8 +369,8 @@ stream32_group_norm_kernel(const float* stream_in, const T* x, int64_t x_stride,
             float4 v = a[k];
             if (x != nullptr) {
                 if (gate != nullptr) {
-                    b[k].x /= 1.0f + expf(-g[k].x), b[k].y /= 1.0f + expf(-g[k].y);
-                    b[k].z /= 1.0f + expf(-g[k].z), b[k].w /= 1.0f + expf(-g[k].w);
+                    b[k].x *= gate_of<T>(g[k].x), b[k].y *= gate_of<T>(g[k].y);
+                    b[k].z *= gate_of<T>(g[k].z), b[k].w *= gate_of<T>(g[k].w);
                 }
                 v = make_float4(v.x + b[k].x, v.y + b[k].y, v.z + b[k].z, v.w + b[k].w);
             }
@@ -386,7 +394,7 @@ stream32_group_norm_kernel(const float* stream_in, const T* x, int64_t x_stride,
             float v = stream_in != nullptr ? stream_in[r * width + c0 + i] : 0.f;
             if (x != nullptr) {
                 float add = to_f<T>(x[r * x_stride + c0 + i]);
-                if (gate != nullptr) add /= 1.0f + expf(-to_f<T>(gate[r * gate_stride + c0 + i]));
+                if (gate != nullptr) add *= gate_of<T>(to_f<T>(gate[r * gate_stride + c0 + i]));
                 v += add;
             }
             if (stream_out != nullptr) stream_out[r * width + c0 + i] = v;
@@ -435,7 +443,9 @@ static void launch_group_norm(const float* stream_in, const void* x, int64_t x_s
 #define TK_GN(ITEMS, VEC)                                                                                          \
     tk_launch(stream32_group_norm_kernel<T, ITEMS, VEC>, grid, block, 0, stream, stream_in, (const T*)x, x_stride,  \
               (const T*)gate, gate_stride, w, eps, stream_out, (T*)y, rows, width, groups)
-    if (vec && gw <= 128 * 2) TK_GN(2, true);
+    if (vec && gw <= 128 * 1) TK_GN(1, true);
+    else if (vec && gw <= 128 * 2) TK_GN(2, true);
+    else if (vec && gw <= 128 * 4) TK_GN(4, true);
     else if (vec && gw <= 128 * 8) TK_GN(8, true);
     else if (gw <= 32 * 8) TK_GN(8, false);
     else TK_GN(0, false);

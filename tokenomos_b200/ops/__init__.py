@@ -1395,11 +1395,13 @@ SSD_MAX_STATE = 256
 
 def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state: torch.Tensor, cu_seqlens: torch.Tensor, seq_ctx: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
-             heads: int, v_dim: int, n_state: int, groups: int) -> torch.Tensor:
+             heads: int, v_dim: int, n_state: int, groups: int, sm_count: int = 148) -> torch.Tensor:
     """The state-space recurrence over a step's tokens: ``dt = softplus(dt_raw + dt_bias)``, ``S_t = exp(-exp(a_log)
     dt) S_(t-1) + dt B_t x_t^T``, ``y_t = S_t^T C_t + d_skip x_t`` per head. ``xbc`` [T, >= heads v_dim + 2 groups
     n_state] (rows may be strided): x, then B, then C; ``dt_raw`` float32 [T, >= heads]; ``state`` float32 [slots,
-    heads, n_state, v_dim]. Returns ``y`` float32 [T, heads v_dim]."""
+    heads, n_state, v_dim]. Returns ``y`` float32 [parts, T, heads v_dim]: a step of few, long portions is walked
+    by several blocks a head, each over a part of the state's rows, and their sums are still to be added
+    (``gated_group_norm`` does; ``y.sum(0)`` is the result)."""
     _cuda(xbc, dt_raw, dt_bias, a_log, d_skip, state)
     T = xbc.shape[0]
     if xbc.stride(1) != 1 or xbc.shape[1] < heads * v_dim + 2 * groups * n_state:
@@ -1408,24 +1410,27 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
         raise KernelError(f"ssd_scan: dt is float32 [{T}, >= {heads}]")
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, n_state, v_dim) or not state.is_contiguous():
         raise KernelError(f"ssd_scan: the state is float32 [slots, {heads}, {n_state}, {v_dim}]")
-    y = torch.empty(T, heads * v_dim, dtype=torch.float32, device=xbc.device)
+    split = _lib.call("tk_ssd_split", T, int(n_seqs), heads, v_dim, n_state, int(sm_count))
+    y = torch.empty(split, T, heads * v_dim, dtype=torch.float32, device=xbc.device)
     _lib.call("tk_ssd_scan", _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(_f32vec(dt_bias, "dt_bias", heads)),
               _ptr(_f32vec(a_log, "A_log", heads)), _ptr(_f32vec(d_skip, "D", heads)), _ptr(state),
               _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")),
-              int(n_seqs), _ptr(y), heads, v_dim, n_state, groups, _dtype_code(xbc), _stream())
+              int(n_seqs), T, _ptr(y), split, heads, v_dim, n_state, groups, _dtype_code(xbc), _stream())
     return y
 
 
 def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, groups: int) -> torch.Tensor:
     """``v = y * silu(z)``, each of the row's ``groups`` equal parts divided by its own ``sqrt(mean(v^2) + eps)``,
-    times ``weight``. ``y`` float32 [T, C], ``z`` [T, C] in the storage type (rows may be strided); returns
-    [T, C] in ``z``'s type."""
+    times ``weight``. ``y`` float32 [T, C], or [parts, T, C] whose parts are added up first; ``z`` [T, C] in the
+    storage type (rows may be strided); returns [T, C] in ``z``'s type."""
     _cuda(y, z, weight)
-    T, C = y.shape
+    if y.dim() == 2:
+        y = y.unsqueeze(0)
+    parts, T, C = y.shape
     if y.dtype != torch.float32 or not y.is_contiguous() or z.stride(1) != 1 or tuple(z.shape) != (T, C):
-        raise KernelError("gated_group_norm: y float32 [T, C] contiguous, z [T, C] with contiguous columns")
+        raise KernelError("gated_group_norm: y float32 [parts, T, C] contiguous, z [T, C] with contiguous columns")
     out = torch.empty(T, C, dtype=z.dtype, device=y.device)
-    _lib.call("tk_gated_group_norm", _ptr(y), _ptr(z), z.stride(0), _ptr(_f32vec(weight, "norm weight", C)), float(eps),
+    _lib.call("tk_gated_group_norm", _ptr(y), parts, _ptr(z), z.stride(0), _ptr(_f32vec(weight, "norm weight", C)), float(eps),
               _ptr(out), T, C, int(groups), _dtype_code(z), _stream())
     return out
 

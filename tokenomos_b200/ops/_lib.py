@@ -100,8 +100,9 @@ _SIGNATURES = {
     "tk_mlstm_scan": [P, L, I, I, I, P, L, F, F, P, P, P, P, P, I, I, P, P, I, I, I, I, P],
     "tk_mlstm_norm_gate": [P, P, P, P, P, L, P, P, P, P, I, I, I, F, I, P],
     "tk_ssd_max_state": [],
-    "tk_ssd_scan": [P, L, P, L, P, P, P, P, P, P, P, I, P, I, I, I, I, I, P],
-    "tk_gated_group_norm": [P, P, L, P, F, P, I, I, I, I, P],
+    "tk_ssd_scan": [P, L, P, L, P, P, P, P, P, P, P, I, I, P, I, I, I, I, I, I, P],
+    "tk_ssd_split": [I, I, I, I, I, I],
+    "tk_gated_group_norm": [P, I, P, L, P, F, P, I, I, I, I, P],
     "tk_qkv_maps_write": [P, L, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, P],
     "tk_diff_combine": [P, P, I, I, F, F, F, I, P],
     "tk_stream32_group_norm": [P, P, L, P, L, P, F, P, P, I, I, I, I, P],
@@ -156,7 +157,7 @@ _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled"
             "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status",
             "tk_attn_latent_rows", "tk_attn_latent_max_rank", "tk_gemm_grouped_tile", "tk_attn_latent_mma_rows",
             "tk_attn_latent_mma_supported", "tk_attn_pointwise_rows", "tk_attn_pointwise_mma_supported",
-            "tk_attn_pointwise_mma_tokens", "tk_ssd_max_state"}
+            "tk_attn_pointwise_mma_tokens", "tk_ssd_max_state", "tk_ssd_split"}
 
 
 _fns: dict = {}

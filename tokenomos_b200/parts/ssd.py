@@ -58,6 +58,7 @@ class StateSpaceDuality:
         self.d_skip = d_skip.float().reshape(-1).contiguous()
         self.norm = norm.float().reshape(-1).contiguous()
         self.tile = max(int(tile), self.K - 1, 1)
+        self.sm_count = in_proj.tuning.sm_count
 
     def state_specs(self) -> dict:
         specs = {"S": SlotState((self.heads, self.state, self.v_dim), torch.float32)}
@@ -73,7 +74,8 @@ class StateSpaceDuality:
                            ctx.cu_seqlens, ctx.seq_ctx, ctx.seq_slot,
                            ctx.tiles(ops.seq_conv_tile(self.tile, T, self.channels)), proj.dtype, act=True)
         y = ops.ssd_scan(xbc, dt, self.dt_bias, self.a_log, self.d_skip, ctx.states[(call, "S")], ctx.cu_seqlens,
-                         ctx.seq_ctx, ctx.seq_slot, ctx.n_seqs, self.heads, self.v_dim, self.state, self.groups)
+                         ctx.seq_ctx, ctx.seq_slot, ctx.n_seqs, self.heads, self.v_dim, self.state, self.groups,
+                         self.sm_count)
         out = ops.gated_group_norm(y, proj[:, :self.inner], self.norm, self.eps, self.norm_groups)
         return self.out_proj(out)
 
