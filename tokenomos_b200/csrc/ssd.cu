@@ -47,8 +47,8 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
     return d;
 }
 
-// XC: values of x a thread keeps for the round ahead (TOK * COLS over the block's threads: 2 with eight
-// slices, 4 with four or more, else 16); 0: nothing is kept ahead, a round's rows go from memory to
+// XC: values of x a thread keeps for the stage ahead (TOK * COLS over the block's threads: 2 with eight
+// slices, 4 with four or more, else 16); 0: nothing is kept ahead, a stage's rows go from memory to
 // shared memory directly, which costs fewer registers and is what a step of single tokens wants.
 template <typename T, int R, int XC>
 __global__ void __launch_bounds__(SSD_COLS* SSD_MAX_SLICES, XC > 0 ? 2 : 4)
@@ -91,7 +91,7 @@ ssd_scan_kernel(const T* xbc, int64_t xbc_stride, const float* dt_raw, int64_t d
         }
     }
 
-    // A round's rows are asked for one round ahead and wait in registers while the round before is
+    // A stage's rows are asked for one stage ahead and wait in registers while the stage before is
     // walked, so that the walk never waits for memory: per thread TOK * R / 32 values of B and of C
     // (TOK * NP of each over 32 * slices threads), up to XC of x, one of dt.
     constexpr int BC = XC > 0 ? SSD_TOK * R / 32 : 1;
@@ -145,7 +145,7 @@ ssd_scan_kernel(const T* xbc, int64_t xbc_stride, const float* dt_raw, int64_t d
             if (tid < nt) rdt = dt_raw[(size_t)(first + t0 + tid) * dt_stride + h];
         }
         if (tid < SSD_TOK) {
-            // (a round's unused tokens leave the state as it is: a step of 0 and a decay of 1)
+            // (a stage's unused tokens leave the state as it is: a step of 0 and a decay of 1)
             const float v = rdt + bias;
             const float dt = tid < nt ? (v > 20.f ? v : log1pf(expf(v))) : 0.f;
             dts[tid] = dt;
@@ -232,7 +232,7 @@ static void launch_ssd_as(const void* xbc, int64_t xbc_stride, const float* dt_r
               seq_ctx, seq_slot, y, y_part, H, V, N, G, split);
 }
 
-// `ahead`: whether rounds are asked for a round ahead (steps with prompt portions)
+// `ahead`: whether stages are asked for a stage ahead (steps with prompt portions)
 template <typename T, int R>
 static int launch_ssd(const void* xbc, int64_t xbc_stride, const float* dt_raw, int64_t dt_stride, const float* dt_bias,
                       const float* A_log, const float* D_skip, float* state, const int* cu_seqlens, const int* seq_ctx,
