@@ -691,6 +691,69 @@ def test_random_configurations(seed, tmp_path):
                     close_calls=0.0 if dtype == "float32" else 0.5)
 
 
+def random_config_wide(seed: int) -> tuple[dict, int]:
+    """Draws among the sizes the tensor-core kernels take in bfloat16 (differential heads of 2 x 32 and 2 x 64 with
+    values as wide, groups of 1 to 8 maps a key head; latents of 64 to 256 with rotated parts of 16 to 64), mixed
+    with sizes they do not take, windows around the page and tile sizes."""
+    import random
+
+    rng = random.Random(1000 + seed)
+    groups = rng.choice([1, 2, 4])
+    width = rng.choice([128, 192, 256])
+    layers, sources = [], {}
+    for i in range(rng.randint(3, 6)):
+        kind = rng.choice(["attention", "mamba2", "latent_attention", "latent_attention"])
+        if kind == "attention":
+            dim = rng.choice([32, 64, 48])
+            kv = rng.choice([1, 2])
+            layer = attention(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([2 * dim, 2 * dim, dim]), dim ** -0.5,
+                              rng.choice([0.2, 0.5, 0.7]), rng.choice([None, 16, 63, 64, 65, 130, 200]))
+        elif kind == "mamba2":
+            g = rng.choice([1, 2, 4])
+            heads, vdim = g * rng.choice([1, 2]), rng.choice([32, 48, 64])
+            layer = mamba(heads, vdim, rng.choice([16, 32, 64, 128]), g, rng.choice([2, 3, 4]), rng.choice([1, 2, heads]))
+        elif sources and rng.random() < 0.5:
+            src = rng.choice(sorted(sources))
+            m = sources[src]
+            layer = latent(rng.choice([2, 4, 8]), rng.choice([32, 64]), m["rot_dim"], rng.choice([32, 48, 64]), rng.choice([48, 80]),
+                           m["kv_rank"], 0.12, m["rot"]["base"], kv_from=src)
+        else:
+            layer = latent(rng.choice([2, 4, 8]), rng.choice([32, 64]), rng.choice([16, 32, 64]), rng.choice([32, 48, 64]),
+                           rng.choice([48, 80, 128]), rng.choice([64, 128, 256]), 0.12, rng.choice([10000.0, 500000.0]))
+            sources[i] = layer["mixer"]
+        pick = rng.random()
+        if pick < 0.15:
+            layer["mlp"] = None
+        elif pick < 0.5:
+            layer["mlp"] = dense(rng.choice([128, 384]))
+        else:
+            experts = rng.choice([4, 8, 16])
+            layer["mlp"] = moe(experts, rng.randint(1, 4), rng.choice([64, 96]), rng.choice([None, 64, 128]))
+        layers.append(layer)
+    config = {"architecture": "Fakelorn", "vocab": rng.randint(300, 600), "width": width,
+              "norm": {"eps": 1e-5, "groups": groups}, "logit_scale": rng.choice([0.2, 0.5]),
+              "logit_softcap": rng.choice([10.0, 30.0]), "layers": layers}
+    return config, 16
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(6))
+def test_random_configurations_at_tensor_core_sizes(seed, tmp_path):
+    config, page = random_config_wide(seed)
+    tensors = make_tensors(config, 700 + seed)
+    write_folder(tmp_path, config, tensors)
+    w = {k: v.double() for k, v in tensors.items()}
+    g = torch.Generator().manual_seed(seed)
+    reqs = {f"r{i}": torch.randint(0, config["vocab"], (n,), generator=g).tolist() for i, n in enumerate([2, 33, 70, 150, 260])}
+    want = {rid: plain.forward(config, w, ids)[0] for rid, ids in reqs.items()}
+    for dtype, tol in (("float32", 8e-5), ("bfloat16", 0.25)):
+        for steps in (trace_util.tail_decoded(reqs, 40), trace_util.mixed(reqs, live=4, seed=seed)):
+            per_step = trace_util.run_in_process(tmp_path, dtype, steps, trace_util.max_live_tokens(steps, page), page,
+                                                 max_requests=4)
+            compare(trace_util.collect(steps, per_step), want, tol, f"wide random configuration {seed} {dtype}: {config}",
+                    close_calls=0.0 if dtype == "float32" else 0.5)
+
+
 @pytest.mark.gpu
 def test_layers_one_by_one(folders):
     """The residual stream after every layer, in 32-bit: a fault shows at the layer that has it."""

@@ -54,7 +54,7 @@ class Fakelorn:
                 mixer = PartSpec("attention", {
                     "heads": 2 * m.heads, "kv_heads": m.kv_heads, "head_dim": 2 * m.dim, "v_dim": m.vdim,
                     "scale": m.scale, "window": m.window, "position": {"kind": "plain", "params": {"maps": 2}},
-                    "diff": {"init": m.diff, "eps": cfg.norm_eps},
+                    "diff": {"init": m.diff, "eps": cfg.norm_eps}, "exact": True,
                 }, {"q": TensorDecl(a + "q", (m.heads * 2 * m.dim, d)), "k": TensorDecl(a + "k", (m.kv_heads * 2 * m.dim, d)),
                     "v": TensorDecl(a + "v", (m.kv_heads * m.vdim, d)), "o": TensorDecl(a + "o", (d, m.heads * m.vdim)), **vec})
             elif layer.kind == "mamba2":
